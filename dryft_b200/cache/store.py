@@ -35,7 +35,11 @@ class KVNeed:
     a key row's ``head_dim`` (a key row may hold several score maps' keys).  ``chunk``: queries only see keys of
     their own block of ``chunk`` positions (blocks aligned to the sequence's start), so pages wholly before the block of the
     next position are given back.  ``values=False``: the mixer keeps one row per token only (a latent that both its keys
-    and its values are made from); no value pages exist and ``CacheEntry.v`` is None."""
+    and its values are made from); no value pages exist and ``CacheEntry.v`` is None.  ``pool``: beside the tokens' rows the
+    mixer keeps ONE key row and one value row per block of ``pool`` positions (what it puts there -- the block's mean, say --
+    is its own business); those rows live in pages of their own that are never given back early, and reach the mixer as
+    ``CacheEntry.pooled``.  With a ``pool``, ``window`` is how many of the last tokens' rows must stay (the mixer's own
+    window or the block it is still to summarise, whichever is longer)."""
 
     kv_heads: int
     head_dim: int
@@ -43,6 +47,7 @@ class KVNeed:
     v_head_dim: Optional[int] = None
     chunk: Optional[int] = None
     values: bool = True
+    pool: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -64,13 +69,19 @@ class CacheEntry:
     page_table: torch.Tensor  # [max_slots, max_pages_per_slot] int32
     page_size: int
     window: Optional[int]
+    # one row per block of positions (``KVNeed.pool``): the same layout, row ``b`` of a sequence being block ``b``;
+    # ``fills_pooled`` says that this run step is the one that writes them (a borrower that summarises the same
+    # blocks as the step it borrows from reads that step's rows)
+    pooled: Optional["CacheEntry"] = None
+    fills_pooled: bool = False
 
 
 class _KVGroup:
     def __init__(self, need: KVNeed, run_steps: List[int], n_pages: int, page_size: int, max_slots: int,
-                 max_pages_per_slot: int, dtype: torch.dtype, device: torch.device, trim: bool = True):
+                 max_pages_per_slot: int, dtype: torch.dtype, device: torch.device, trim: bool = True, unit: int = 1):
         self.need = need
         self.run_steps = run_steps
+        self.unit = unit     # positions per row: 1 for the tokens' own rows, the block size for pooled rows
         # ``trim`` is off when a run step that borrows this group's entries sees keys another way than the owners do:
         # what the owners could give back, the borrower may still read
         self.trims = trim and (need.window is not None or need.chunk is not None)
@@ -163,6 +174,32 @@ class SequenceCache:
                     self._entry_of[i] = self._entry_of[src]
                 if src in self._states:
                     self._states[i] = self._states[src]
+        # pooled rows (one per block of ``pool`` positions): a run step that asks for them fills an entry of its own, except
+        # a borrower that summarises the same blocks as the step it borrows from, which reads that step's rows
+        self._pooled_of: Dict[int, Tuple[int, int, bool]] = {}   # run step -> (group index, index in group, fills it)
+        by_pool: Dict[KVNeed, List[int]] = {}
+        for i, (kv, _) in enumerate(needs):
+            if kv is None or kv.pool is None or i not in self._entry_of:
+                continue
+            if kv.pool <= 0:
+                raise CacheError(f"run step {i}: KVNeed.pool must be positive, got {kv.pool}")
+            src = borrow[i]
+            if src is not None and needs[src][0] is not None and needs[src][0].pool == kv.pool:
+                continue
+            by_pool.setdefault(KVNeed(kv.kv_heads, kv.head_dim, None, kv.v_head_dim, None, kv.values, kv.pool), []).append(i)
+        for need, steps in by_pool.items():
+            rows = max_tokens // need.pool
+            pool_pages = pages_for(rows, page_size) + max_slots       # every sequence may leave its last page partly empty
+            per_slot = max(1, min(pages_for(max_seq_len // need.pool, page_size), pool_pages))
+            g = _KVGroup(need, steps, pool_pages, page_size, max_slots, per_slot, dtype, device, trim=False, unit=need.pool)
+            for j, s in enumerate(steps):
+                self._pooled_of[s] = (len(self._groups), j, True)
+            self._groups.append(g)
+        for i, src in enumerate(borrow):
+            if src is not None and i not in self._pooled_of and src in self._pooled_of and needs[i][0] is not None \
+                    and needs[i][0].pool is not None:
+                gi, j, _ = self._pooled_of[src]
+                self._pooled_of[i] = (gi, j, False)
 
     # ------------------------------------------------------------------ views for the parts
     def entry(self, run_step: int) -> Optional[CacheEntry]:
@@ -170,7 +207,13 @@ class SequenceCache:
         if loc is None:
             return None
         g = self._groups[loc[0]]
-        return CacheEntry(g.k[loc[1]], g.v[loc[1]] if g.v is not None else None, g.page_table, self.page_size, g.need.window)
+        entry = CacheEntry(g.k[loc[1]], g.v[loc[1]] if g.v is not None else None, g.page_table, self.page_size, g.need.window)
+        ploc = self._pooled_of.get(run_step)
+        if ploc is not None:
+            pg = self._groups[ploc[0]]
+            entry.pooled = CacheEntry(pg.k[ploc[1]], pg.v[ploc[1]] if pg.v is not None else None, pg.page_table, self.page_size, None)
+            entry.fills_pooled = ploc[2]
+        return entry
 
     def state(self, run_step: int):
         """The run step's state ``[slots, *shape]`` (a mapping of such tensors if it asked with a mapping), or None."""
@@ -197,7 +240,7 @@ class SequenceCache:
         """Tokens the scarcest group could still take."""
         if not self._groups:
             return self.max_tokens
-        return min(g.ledger.pool.n_free for g in self._groups) * self.page_size
+        return min(g.ledger.pool.n_free * g.unit for g in self._groups) * self.page_size
 
     # ------------------------------------------------------------------ sequences
     def open_sequences(self, n: int) -> List[int]:
@@ -234,8 +277,7 @@ class SequenceCache:
             return False
         if any(n > self.max_seq_len for n in lengths):
             return False
-        need = sum(pages_for(n, self.page_size) for n in lengths)
-        return all(need <= g.ledger.pool.n_free for g in self._groups)
+        return all(sum(pages_for(n // g.unit, self.page_size) for n in lengths) <= g.ledger.pool.n_free for g in self._groups)
 
     def reserve(self, slot: int, n_new: int) -> None:
         """Make room for ``n_new`` more tokens of ``slot`` in every group (host side; the page
@@ -249,14 +291,15 @@ class SequenceCache:
         # all-or-nothing over the groups: check before taking
         for g in self._groups:
             held = g.ledger.held(slot)
-            want = [lp for lp in range(pages_for(cur, self.page_size), pages_for(new, self.page_size)) if lp not in held]
+            want = [lp for lp in range(pages_for(cur // g.unit, self.page_size), pages_for(new // g.unit, self.page_size))
+                    if lp not in held]
             if len(want) > g.ledger.pool.n_free:
                 raise CacheError(
                     f"cache full: {len(want)} more page(s) of {self.page_size} tokens wanted, "
                     f"{g.ledger.pool.n_free} free (built for {self.max_tokens} tokens)"
                 )
         for g in self._groups:
-            added = g.ledger.grow(slot, cur, new)
+            added = g.ledger.grow(slot, cur // g.unit, new // g.unit)
             if added:
                 row = g.page_table_host[slot]
                 for lp, pp in added.items():

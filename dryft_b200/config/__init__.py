@@ -4,6 +4,7 @@ from .spec import ExtraPart, LayerSpec, ModelSpec, PartSpec, RunStep
 from .qwen3 import ConfigError, Qwen3Config
 from .tevovik import TevovikConfig
 from .vobusun import VobusunConfig
+from .mogelix import MogelixConfig
 from .registry import (
     Architecture,
     architecture_of,
@@ -19,10 +20,11 @@ from .presets import PRESETS, preset
 register_architecture("Qwen3ForCausalLM", Qwen3Config.from_dict)
 register_architecture("Tevovik", TevovikConfig.from_dict)
 register_architecture("Vobusun", VobusunConfig.from_dict)
+register_architecture("Mogelix", MogelixConfig.from_dict)
 
 __all__ = [
     "ExtraPart",
-    "Architecture", "ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "PRESETS", "Qwen3Config", "RunStep", "TevovikConfig", "VobusunConfig",
+    "Architecture", "ConfigError", "LayerSpec", "ModelSpec", "MogelixConfig", "PartSpec", "PRESETS", "Qwen3Config", "RunStep", "TevovikConfig", "VobusunConfig",
     "architecture_of", "config_from_dict", "known_architectures", "load_config", "load_model_spec",
     "preset", "register_architecture", "unregister_architecture",
 ]

@@ -4,7 +4,8 @@
 //                 (contiguous, equally sized); a group is ranked by the maximum score among its members, and selection
 //                 is restricted to the `keep` highest-ranked groups
 //                 (n_groups = keep = 1: no groups).  The `top` allowed experts with the largest scores are chosen;
-//                 their weights are the scores themselves, or the scores divided by their sum (`renorm`).
+//                 their weights are the scores themselves, or the scores divided by their sum (`renorm`: the softmax
+//                 over the chosen logits only).  `bias` (optional, [E]) is added to the logits first.
 //                 Ties go to the lower index.  One warp per token.  moe_route_rows is the same for few tokens with the
 //                 router's product inside (one block per token, one launch instead of two).
 //   moe_rows      an assignment a = (token, k) multiplies its token's activation row by its expert's matrices, every
@@ -12,6 +13,7 @@
 //                 tokens (decode) and for the 32-bit path.
 //                   mode 0:  act[a, f] = silu(Wg_e[f] . h[token]) * (Wu_e[f] . h[token])      (W_gu [E, 2F, K]: gate rows, then up rows)
 //                   mode 1:  y[a, c]   = Wd_e[c] . act[a]                                    (W_d [E, C, F])
+//                   mode 2:  act[a, f] = max(Wu_e[f] . h[token], 0)^2                         (W_u [E, F, K]: experts without a gate)
 //                 32-bit accumulation in a fixed order, one rounding to T at the end.
 //   moe_combine   out[n] = sum_k wts[n, k] * y[n*top + k]   (32-bit sum, rounded once) for callers that do not fold the
 //                 weighted sum into a kernel of their own.
@@ -33,14 +35,15 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 
 // One warp's choice for one token: z holds the E logits (global or shared memory), s and gs are the warp's scratch
 // ([E] scores, [n_groups] group scores) in shared memory.
-__device__ __forceinline__ void route_one(const float* z, float* s, float* gs, int lane, int n, int E, int n_groups, int keep,
-                                          int top, int renorm, int* __restrict__ idx_out, float* __restrict__ w_out) {
+__device__ __forceinline__ void route_one(const float* z, const float* __restrict__ bias, float* s, float* gs, int lane, int n, int E,
+                                          int n_groups, int keep, int top, int renorm, int* __restrict__ idx_out,
+                                          float* __restrict__ w_out) {
   float mx = -INFINITY;
-  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e] + (bias != nullptr ? bias[e] : 0.f));
   mx = warp_max(mx);
   float sum = 0.f;
   for (int e = lane; e < E; e += 32) {
-    const float p = expf(z[e] - mx);
+    const float p = expf(z[e] + (bias != nullptr ? bias[e] : 0.f) - mx);
     s[e] = p;
     sum += p;
   }
@@ -92,14 +95,14 @@ __device__ __forceinline__ void route_one(const float* z, float* s, float* gs, i
 }
 
 __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(
-    const float* __restrict__ logits, int n_tokens, int E, int n_groups, int keep, int top, int renorm,
+    const float* __restrict__ logits, const float* __restrict__ bias, int n_tokens, int E, int n_groups, int keep, int top, int renorm,
     int* __restrict__ idx_out, float* __restrict__ w_out) {
   extern __shared__ float sm[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * ROUTE_WARPS + warp;
   if (n >= n_tokens) return;
   float* s = sm + (size_t)warp * (E + n_groups);
-  route_one(logits + (size_t)n * E, s, s + E, lane, n, E, n_groups, keep, top, renorm, idx_out, w_out);
+  route_one(logits + (size_t)n * E, bias, s, s + E, lane, n, E, n_groups, keep, top, renorm, idx_out, w_out);
 }
 
 // Few tokens (decode): the router's product and its choice in one launch.  One block per token: the token's row is staged
@@ -107,8 +110,8 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(
 constexpr int ROUTE_ROW_THREADS = 1024;   // 32 warps: one or two experts a warp keeps the block one or two trips to memory long
 template <typename T>
 __global__ void __launch_bounds__(ROUTE_ROW_THREADS) moe_route_rows_kernel(
-    const T* __restrict__ h, const T* __restrict__ w_router, int K, int E, int n_groups, int keep, int top, int renorm,
-    int* __restrict__ idx_out, float* __restrict__ w_out) {
+    const T* __restrict__ h, const T* __restrict__ w_router, const float* __restrict__ bias, int K, int E, int n_groups, int keep, int top,
+    int renorm, int* __restrict__ idx_out, float* __restrict__ w_out) {
   extern __shared__ __align__(16) unsigned char smraw[];
   T* xs = reinterpret_cast<T*>(smraw);                  // the token's row
   float* z = reinterpret_cast<float*>(smraw + (sizeof(T) * (size_t)K + 15) / 16 * 16);   // [E] logits, [E] scores, [n_groups]
@@ -135,7 +138,7 @@ __global__ void __launch_bounds__(ROUTE_ROW_THREADS) moe_route_rows_kernel(
     if (lane == 0) z[e] = d;
   }
   __syncthreads();
-  if (warp == 0) route_one(z, z + E, z + 2 * E, lane, n, E, n_groups, keep, top, renorm, idx_out, w_out);
+  if (warp == 0) route_one(z, bias, z + E, z + 2 * E, lane, n, E, n_groups, keep, top, renorm, idx_out, w_out);
 }
 
 constexpr int ROWS_THREADS = 128;
@@ -207,6 +210,7 @@ __global__ void __launch_bounds__(ROWS_THREADS) moe_rows_kernel(
     for (int f = 0; f < 2; ++f) {
       float v = warp_sum(d[f][0]);
       if (mode == 0) v = v / (1.f + expf(-v)) * warp_sum(d[f][1]);
+      if (mode == 2) { v = fmaxf(v, 0.f); v *= v; }
       if (lane == 0 && (f == 0 || two)) out[(size_t)a * n_out + o + f] = from_f32<T>(v);
     }
   }
@@ -226,7 +230,7 @@ template <typename T>
 int rows_launch(const void* a_in, int a_div, const void* w, const int* idx, int E, int K, int n_out, int mode, void* out,
                 int n_assign, cudaStream_t st) {
   if (n_assign <= 0) return 0;
-  if (E < 1 || K < 1 || n_out < 1 || a_div < 1 || (mode != 0 && mode != 1)) return DRYFT_ERR_UNSUPPORTED;
+  if (E < 1 || K < 1 || n_out < 1 || a_div < 1 || mode < 0 || mode > 2) return DRYFT_ERR_UNSUPPORTED;
   const size_t smem = (sizeof(T) * (size_t)K + 15) / 16 * 16;
   if (smem > 200 * 1024) return DRYFT_ERR_UNSUPPORTED;
   if (smem > 48 * 1024) {
@@ -242,13 +246,13 @@ int rows_launch(const void* a_in, int a_div, const void* w, const int* idx, int 
 }
 }  // namespace
 
-DRYFT_API int dryft_moe_route(const float* logits, int n_tokens, int E, int n_groups, int keep, int top, int renorm,
+DRYFT_API int dryft_moe_route(const float* logits, const float* bias, int n_tokens, int E, int n_groups, int keep, int top, int renorm,
                               int* idx_out, float* w_out, cudaStream_t st) {
   if (n_tokens <= 0) return 0;
   if (E < 1 || top < 1 || top > E || n_groups < 1 || E % n_groups || keep < 1 || keep > n_groups) return DRYFT_ERR_UNSUPPORTED;
   const size_t smem = sizeof(float) * (size_t)ROUTE_WARPS * (E + n_groups);
   if (smem > 48 * 1024) return DRYFT_ERR_UNSUPPORTED;
-  moe_route_kernel<<<(n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS, ROUTE_WARPS * 32, smem, st>>>(logits, n_tokens, E, n_groups, keep,
+  moe_route_kernel<<<(n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS, ROUTE_WARPS * 32, smem, st>>>(logits, bias, n_tokens, E, n_groups, keep,
                                                                                                top, renorm, idx_out, w_out);
   return launch_status();
 }
@@ -268,7 +272,7 @@ DRYFT_API int dryft_moe_combine(int is_bf16, const void* y, const float* wts, in
   return launch_status();
 }
 
-DRYFT_API int dryft_moe_route_rows(int is_bf16, const void* h, const void* w_router, int n_tokens, int K, int E, int n_groups,
+DRYFT_API int dryft_moe_route_rows(int is_bf16, const void* h, const void* w_router, const float* bias, int n_tokens, int K, int E, int n_groups,
                                    int keep, int top, int renorm, int* idx_out, float* w_out, cudaStream_t st) {
   if (n_tokens <= 0) return 0;
   if (E < 1 || top < 1 || top > E || n_groups < 1 || E % n_groups || keep < 1 || keep > n_groups || K < 1) return DRYFT_ERR_UNSUPPORTED;
@@ -276,9 +280,9 @@ DRYFT_API int dryft_moe_route_rows(int is_bf16, const void* h, const void* w_rou
   if (smem > 48 * 1024) return DRYFT_ERR_UNSUPPORTED;
   if (is_bf16)
     moe_route_rows_kernel<__nv_bfloat16><<<n_tokens, ROUTE_ROW_THREADS, smem, st>>>((const __nv_bfloat16*)h, (const __nv_bfloat16*)w_router,
-                                                                                    K, E, n_groups, keep, top, renorm, idx_out, w_out);
+                                                                                    bias, K, E, n_groups, keep, top, renorm, idx_out, w_out);
   else
-    moe_route_rows_kernel<float><<<n_tokens, ROUTE_ROW_THREADS, smem, st>>>((const float*)h, (const float*)w_router, K, E, n_groups, keep,
+    moe_route_rows_kernel<float><<<n_tokens, ROUTE_ROW_THREADS, smem, st>>>((const float*)h, (const float*)w_router, bias, K, E, n_groups, keep,
                                                                             top, renorm, idx_out, w_out);
   return launch_status();
 }

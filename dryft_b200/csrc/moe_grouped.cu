@@ -86,6 +86,7 @@ __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(
 
 // MODE 0: A rows are h[perm[p] / top], B is W_gu[e] ([2F, K]: gate rows then up rows), out is act[p, F]
 // MODE 1: A rows are act[p],           B is W_d[e]  ([C, K]),                        out is y[perm[p], C]
+// MODE 2: A rows are h[perm[p] / top], B is W_u[e]  ([F, K]: experts without a gate), out is act[p, F] = max(., 0)^2
 // A block of 2 x 2 warps computes BM sorted rows x BN output columns (of gate AND up in mode 0), a warp BM/2 x BN/2.
 template <int MODE, int BM, int BN>
 __global__ void __launch_bounds__(128) moe_grouped_kernel(
@@ -111,7 +112,7 @@ __global__ void __launch_bounds__(128) moe_grouped_kernel(
   const int wm = warp >> 1, wn = warp & 1;
   const int g = lane >> 2, t = lane & 3;
 
-  for (int r = tid; r < BM; r += NTHREADS) row_src[r] = r < rows ? (MODE == 0 ? perm[p0 + r] / top : p0 + r) : -1;
+  for (int r = tid; r < BM; r += NTHREADS) row_src[r] = r < rows ? (MODE != 1 ? perm[p0 + r] / top : p0 + r) : -1;
   __syncthreads();
   const bf16* we = w + (size_t)e * (NMAT * n_out) * K;
 
@@ -186,7 +187,7 @@ __global__ void __launch_bounds__(128) moe_grouped_kernel(
   for (int i = 0; i < MT; ++i) {
     const int r0 = wm * WM + i * 16 + g, r1 = r0 + 8;
     size_t o0 = 0, o1 = 0;
-    if (MODE == 0) {
+    if (MODE != 1) {
       o0 = (size_t)(p0 + r0) * n_out;
       o1 = (size_t)(p0 + r1) * n_out;
     } else {
@@ -203,6 +204,10 @@ __global__ void __launch_bounds__(128) moe_grouped_kernel(
         v1 = v1 / (1.f + expf(-v1)) * acc[NMAT - 1][i][j][1];
         v2 = v2 / (1.f + expf(-v2)) * acc[NMAT - 1][i][j][2];
         v3 = v3 / (1.f + expf(-v3)) * acc[NMAT - 1][i][j][3];
+      }
+      if (MODE == 2) {
+        v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); v2 = fmaxf(v2, 0.f); v3 = fmaxf(v3, 0.f);
+        v0 *= v0; v1 *= v1; v2 *= v2; v3 *= v3;
       }
       if (r0 < rows) *reinterpret_cast<unsigned*>(out + o0 + c) = pack_bf16(v0, v1);
       if (r1 < rows) *reinterpret_cast<unsigned*>(out + o1 + c) = pack_bf16(v2, v3);
@@ -252,8 +257,9 @@ DRYFT_API long long dryft_moe_grouped_work_ints(int n_assign, int E) {
 }
 
 // y[n*top, C] = experts of idx[n, top] applied to h[n, W]; act [n*top, F] is scratch (sorted order)
+// `gated`: 1 = w_gate_up is [E, 2F, W] and the activation is silu(gate) * up; 0 = it is [E, F, W] and the activation is max(., 0)^2
 DRYFT_API int dryft_moe_grouped(const void* h, const void* w_gate_up, const void* w_down, const int* idx, int n_tokens, int top,
-                                int E, int W, int F, void* act, void* y, int* work, cudaStream_t st) {
+                                int E, int W, int F, void* act, void* y, int* work, int gated, cudaStream_t st) {
   if (n_tokens <= 0) return 0;
   if (top < 1 || E < 1 || W % 16 || F % 16 || W < 16 || F < 16) return DRYFT_ERR_UNSUPPORTED;
   const long long n_assign_ll = (long long)n_tokens * top;
@@ -270,11 +276,13 @@ DRYFT_API int dryft_moe_grouped(const void* h, const void* w_gate_up, const void
   int rc = launch_status();
   if (rc) return rc;
   if (bm == 128) {
-    rc = gemm_launch<0, 128, 64>(h, w_gate_up, offsets, perm, tile_expert, tile_row0, n_tiles, top, W, F, act, max_tiles, st);
+    rc = gated ? gemm_launch<0, 128, 64>(h, w_gate_up, offsets, perm, tile_expert, tile_row0, n_tiles, top, W, F, act, max_tiles, st)
+               : gemm_launch<2, 128, 64>(h, w_gate_up, offsets, perm, tile_expert, tile_row0, n_tiles, top, W, F, act, max_tiles, st);
     if (rc) return rc;
     return gemm_launch<1, 128, 128>(act, w_down, offsets, perm, tile_expert, tile_row0, n_tiles, top, F, W, y, max_tiles, st);
   }
-  rc = gemm_launch<0, 64, 64>(h, w_gate_up, offsets, perm, tile_expert, tile_row0, n_tiles, top, W, F, act, max_tiles, st);
+  rc = gated ? gemm_launch<0, 64, 64>(h, w_gate_up, offsets, perm, tile_expert, tile_row0, n_tiles, top, W, F, act, max_tiles, st)
+             : gemm_launch<2, 64, 64>(h, w_gate_up, offsets, perm, tile_expert, tile_row0, n_tiles, top, W, F, act, max_tiles, st);
   if (rc) return rc;
   return gemm_launch<1, 64, 128>(act, w_down, offsets, perm, tile_expert, tile_row0, n_tiles, top, F, W, y, max_tiles, st);
 }

@@ -1,0 +1,158 @@
+// A selective state-space mixer (state-space duality form), all of it in 32-bit.
+//
+// The mixer's input product leaves, per token, [z | x (heads * dv) | B (groups * N) | C (groups * N) | dt (heads)] as
+// floats (row stride ld).  x, B and C ("xbc", CH channels from column x_off) pass a short causal convolution per channel
+// and silu; then per head h (its B and C are those of group h / (heads / groups)):
+//
+//     dt_t = softplus(dt_t + dt_bias_h) ;  S_t = exp(-exp(A_log_h) dt_t) S_(t-1) + dt_t B_t x_t^T ;  y_t = S_t^T C_t + D_h x_t
+//
+// with S an N x dv matrix per head.  Per-sequence state, indexed by cache slot and zero when a sequence starts: S
+// [slots, heads, N, dv], and the convolution's last taps - 1 inputs `tail` [slots, taps - 1, CH].  A prompt, a piece of
+// one and a single token are the same operation.
+//
+//   ssm_conv    out[t, c] = silu(cb[c] + sum_j cw[c, j] * in[t - (taps - 1) + j, c]); inputs before the step's first
+//               token come from the tail (zeros before the sequence's start).  One block per token.
+//   ssm_tail    the tail after the step (run after ssm_conv, which reads the old one).  One block per sequence.
+//   ssm_scan    one block per (sequence, head, slice of WARPS value columns); a warp owns one column p of S, a lane the
+//               rows n = lane, lane + 32, ...; tokens in order, the next token's operands requested before the current
+//               token's arithmetic; y_t[p] is a warp sum.
+// Sequences with slot -1 (padding) are skipped.  No block waits on another block.
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+constexpr int CONV_THREADS = 128;
+constexpr int SCAN_WARPS = 4;
+constexpr int MAX_NR = 8;      // state rows a lane holds: N <= 256
+constexpr int MAX_TAPS = 16;
+
+__device__ __forceinline__ int seq_of(const int* __restrict__ cu_q, int n_seqs, int t) {
+  int lo = 0, hi = n_seqs - 1;        // largest b with cu_q[b] <= t
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (cu_q[mid] <= t) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+__global__ void __launch_bounds__(CONV_THREADS) ssm_conv_kernel(
+    const float* __restrict__ proj, int ld, int x_off, int CH, const int* __restrict__ cu_q, const int* __restrict__ seq_slot,
+    int n_seqs, const float* __restrict__ cw, const float* __restrict__ cb, int taps, const float* __restrict__ tail,
+    float* __restrict__ out) {
+  const int t = blockIdx.x;
+  const int b = seq_of(cu_q, n_seqs, t);
+  const int slot = seq_slot[b];
+  if (slot < 0) return;
+  const int i = t - cu_q[b];          // index of the token within this step's part of its sequence
+  for (int c = threadIdx.x; c < CH; c += CONV_THREADS) {
+    float acc = cb[c];
+    for (int j = 0; j < taps; ++j) {
+      const int back = taps - 1 - j, src = i - back;
+      const float v = src >= 0 ? proj[(size_t)(t - back) * ld + x_off + c]
+                               : tail[((size_t)slot * (taps - 1) + (taps - 1 + src)) * CH + c];
+      acc = fmaf(cw[(size_t)c * taps + j], v, acc);
+    }
+    out[(size_t)t * CH + c] = acc / (1.f + expf(-acc));
+  }
+}
+
+__global__ void __launch_bounds__(CONV_THREADS) ssm_tail_kernel(
+    const float* __restrict__ proj, int ld, int x_off, int CH, const int* __restrict__ cu_q, const int* __restrict__ seq_slot,
+    int taps, float* __restrict__ tail) {
+  const int b = blockIdx.x;
+  const int slot = seq_slot[b];
+  if (slot < 0) return;
+  const int t0 = cu_q[b], q = cu_q[b + 1] - t0;
+  if (q <= 0) return;
+  float* tl = tail + (size_t)slot * (taps - 1) * CH;
+  for (int c = threadIdx.x; c < CH; c += CONV_THREADS) {
+    // ascending k: an old entry is read at k + q > k, before it is overwritten
+    for (int k = 0; k < taps - 1; ++k) {
+      const int src = q - (taps - 1) + k;
+      tl[(size_t)k * CH + c] = src >= 0 ? proj[(size_t)(t0 + src) * ld + x_off + c] : tl[(size_t)(k + q) * CH + c];
+    }
+  }
+}
+
+__device__ __forceinline__ float softplusf_(float v) { return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v))); }
+
+__global__ void __launch_bounds__(SCAN_WARPS * 32) ssm_scan_kernel(
+    const float* __restrict__ xbc, int CH, const float* __restrict__ proj, int ld, int dt_off, const float* __restrict__ dt_bias,
+    const float* __restrict__ a_log, const float* __restrict__ Dp, const int* __restrict__ cu_q, const int* __restrict__ seq_slot,
+    int heads, int groups, int N, int dv, float* __restrict__ state, float* __restrict__ y) {
+  const int b = blockIdx.x, hd = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int p = blockIdx.z * SCAN_WARPS + warp;
+  const int slot = seq_slot[b];
+  if (slot < 0 || p >= dv) return;
+  const int t0 = cu_q[b], t1 = cu_q[b + 1];
+  if (t1 <= t0) return;
+  const int inner = heads * dv, g = hd / (heads / groups);
+  const int xo = hd * dv + p, bo = inner + g * N, co = inner + groups * N + g * N;
+  const float rate = expf(a_log[hd]), bias = dt_bias[hd], dskip = Dp[hd];
+  float* sp = state + (((size_t)slot * heads + hd) * N) * dv + p;
+  float S[MAX_NR];
+#pragma unroll
+  for (int r = 0; r < MAX_NR; ++r) {
+    const int n = lane + 32 * r;
+    S[r] = n < N ? sp[(size_t)n * dv] : 0.f;
+  }
+  float Bn[MAX_NR], Cn[MAX_NR], xv, dtr;
+  auto fetch = [&](int t) {
+    const float* row = xbc + (size_t)t * CH;
+#pragma unroll
+    for (int r = 0; r < MAX_NR; ++r) {
+      const int n = lane + 32 * r;
+      Bn[r] = n < N ? row[bo + n] : 0.f;
+      Cn[r] = n < N ? row[co + n] : 0.f;
+    }
+    xv = row[xo];
+    dtr = proj[(size_t)t * ld + dt_off + hd];
+  };
+  fetch(t0);
+  for (int t = t0; t < t1; ++t) {
+    float Bc[MAX_NR], Cc[MAX_NR];
+#pragma unroll
+    for (int r = 0; r < MAX_NR; ++r) { Bc[r] = Bn[r]; Cc[r] = Cn[r]; }
+    const float x = xv, dt = softplusf_(dtr + bias);
+    if (t + 1 < t1) fetch(t + 1);
+    const float decay = expf(-rate * dt), dx = dt * x;
+    float acc = 0.f;
+#pragma unroll
+    for (int r = 0; r < MAX_NR; ++r) {
+      S[r] = fmaf(decay, S[r], Bc[r] * dx);
+      acc = fmaf(S[r], Cc[r], acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) y[(size_t)t * inner + xo] = fmaf(dskip, x, acc);
+  }
+#pragma unroll
+  for (int r = 0; r < MAX_NR; ++r) {
+    const int n = lane + 32 * r;
+    if (n < N) sp[(size_t)n * dv] = S[r];
+  }
+}
+}  // namespace
+
+DRYFT_API int dryft_ssm_conv(const float* proj, int ld, int x_off, int CH, const int* cu_q, const int* seq_slot, int n_seqs,
+                             const float* cw, const float* cb, int taps, float* tail, float* out, int n_tokens, cudaStream_t st) {
+  if (n_tokens <= 0 || n_seqs <= 0) return 0;
+  if (taps < 1 || taps > MAX_TAPS || CH < 1 || (taps > 1 && tail == nullptr)) return DRYFT_ERR_UNSUPPORTED;
+  ssm_conv_kernel<<<n_tokens, CONV_THREADS, 0, st>>>(proj, ld, x_off, CH, cu_q, seq_slot, n_seqs, cw, cb, taps, tail, out);
+  int rc = launch_status();
+  if (rc || taps == 1) return rc;
+  ssm_tail_kernel<<<n_seqs, CONV_THREADS, 0, st>>>(proj, ld, x_off, CH, cu_q, seq_slot, taps, tail);
+  return launch_status();
+}
+
+DRYFT_API int dryft_ssm_scan(const float* xbc, int CH, const float* proj, int ld, int dt_off, const float* dt_bias, const float* a_log,
+                             const float* Dp, const int* cu_q, const int* seq_slot, int n_seqs, int heads, int groups, int N, int dv,
+                             float* state, float* y, cudaStream_t st) {
+  if (n_seqs <= 0) return 0;
+  if (heads < 1 || groups < 1 || heads % groups || N < 1 || N > 32 * MAX_NR || dv < 1 || heads > 65535) return DRYFT_ERR_UNSUPPORTED;
+  dim3 grid(n_seqs, heads, (dv + SCAN_WARPS - 1) / SCAN_WARPS);
+  if (grid.z > 65535) return DRYFT_ERR_UNSUPPORTED;
+  ssm_scan_kernel<<<grid, SCAN_WARPS * 32, 0, st>>>(xbc, CH, proj, ld, dt_off, dt_bias, a_log, Dp, cu_q, seq_slot, heads, groups, N, dv,
+                                                   state, y);
+  return launch_status();
+}

@@ -68,10 +68,10 @@ def core() -> ctypes.CDLL:
             lib.dryft_stream_norm_add.argtypes = [_i, _p, _p, _i, _p, _f, _f, _p, _p, _i, _i, _p]
             lib.dryft_stream_norm_rows.argtypes = [_i, _i, _p, _p, _p, _f, _f, _p, _i, _i, _p]
             lib.dryft_kv_maps_store.argtypes = [_i, _p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p]
-            lib.dryft_moe_route.argtypes = [_p, _i, _i, _i, _i, _i, _i, _p, _p, _p]
+            lib.dryft_moe_route.argtypes = [_p, _p, _i, _i, _i, _i, _i, _i, _p, _p, _p]
             lib.dryft_moe_rows.argtypes = [_i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _i, _p]
             lib.dryft_moe_combine.argtypes = [_i, _p, _p, _i, _i, _p, _i, _p]
-            lib.dryft_moe_route_rows.argtypes = [_i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p]
+            lib.dryft_moe_route_rows.argtypes = [_i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p]
             for name in ("dryft_step_meta", "dryft_step_advance", "dryft_tokens_from_state", "dryft_embed",
                          "dryft_rmsnorm", "dryft_residual_add", "dryft_silu_mul", "dryft_qk_norm_rope_store", "dryft_rope_table",
                          "dryft_gemm_nt_f32", "dryft_argmax_rows", "dryft_sample_rows", "dryft_gemm_small_m", "dryft_row_sumsq",
@@ -760,13 +760,16 @@ def diff_attn_rows(q, k_pages, v_pages, page_table, tok_slot, tok_pos, out, scal
 
 
 # ----------------------------------------------------------------------------- mixture of experts
-def moe_route(logits, n_groups: int, keep: int, top: int, idx_out, w_out, renorm: bool = False) -> None:
-    """The router's choice per token from 32-bit ``logits [n, experts]``: ``idx_out [n, top]`` int32, ``w_out [n, top]`` float32."""
+def moe_route(logits, n_groups: int, keep: int, top: int, idx_out, w_out, renorm: bool = False, bias=None) -> None:
+    """The router's choice per token from 32-bit ``logits [n, experts]`` (plus ``bias [experts]``, if given): ``idx_out [n, top]``
+    int32, ``w_out [n, top]`` float32.  ``renorm``: the chosen scores divided by their sum (a softmax over the chosen logits)."""
     n, e = logits.shape
     _need(logits, "router logits", torch.float32)
+    if bias is not None:
+        _need(bias, "router bias", torch.float32, (e,))
     _need(idx_out, "idx_out", torch.int32, (n, top))
     _need(w_out, "w_out", torch.float32, (n, top))
-    _ok(core().dryft_moe_route(_ptr(logits), n, e, int(n_groups), int(keep), int(top), int(renorm), _ptr(idx_out), _ptr(w_out),
+    _ok(core().dryft_moe_route(_ptr(logits), _ptr(bias), n, e, int(n_groups), int(keep), int(top), int(renorm), _ptr(idx_out), _ptr(w_out),
                                _stream()), f"moe_route ({e} experts, {n_groups} groups, keep {keep}, top {top})")
 
 
@@ -775,7 +778,7 @@ def moe_route_rows_supported(hidden: int, experts: int, groups: int, itemsize: i
     return 4 * (2 * experts + groups) + (itemsize * hidden + 15) // 16 * 16 <= 48 * 1024
 
 
-def moe_route_rows(h, w_router, n_groups: int, keep: int, top: int, idx_out, w_out, renorm: bool = False) -> None:
+def moe_route_rows(h, w_router, n_groups: int, keep: int, top: int, idx_out, w_out, renorm: bool = False, bias=None) -> None:
     """``moe_route`` of ``logits = h @ w_router.T`` (32-bit sums) in one launch, for few tokens: one block per token."""
     n, k = h.shape
     e = w_router.shape[0]
@@ -783,14 +786,17 @@ def moe_route_rows(h, w_router, n_groups: int, keep: int, top: int, idx_out, w_o
     _need(w_router, "router weight", h.dtype, (e, k))
     _need(idx_out, "idx_out", torch.int32, (n, top))
     _need(w_out, "w_out", torch.float32, (n, top))
-    _ok(core().dryft_moe_route_rows(_act(h, "h"), _ptr(h), _ptr(w_router), n, k, e, int(n_groups), int(keep), int(top), int(renorm),
+    if bias is not None:
+        _need(bias, "router bias", torch.float32, (e,))
+    _ok(core().dryft_moe_route_rows(_act(h, "h"), _ptr(h), _ptr(w_router), _ptr(bias), n, k, e, int(n_groups), int(keep), int(top), int(renorm),
                                     _ptr(idx_out), _ptr(w_out), _stream()), f"moe_route_rows ({e} experts over {k})")
 
 
 def moe_rows(a, w, idx, out, mode: str) -> None:
     """Experts evaluated assignment by assignment.  ``idx [n, top]`` int32 names each assignment's expert.
     ``mode="gate_up"``: ``a [n, K]`` token rows, ``w [E, 2F, K]``, ``out [n*top, F] = silu(gate) * up``;
-    ``mode="down"``: ``a [n*top, F]``, ``w [E, C, F]``, ``out [n*top, C]``."""
+    ``mode="down"``: ``a [n*top, F]``, ``w [E, C, F]``, ``out [n*top, C]``;
+    ``mode="up_relu2"`` (experts without a gate): ``a [n, K]``, ``w [E, F, K]``, ``out [n*top, F] = max(up, 0)^2``."""
     n_assign = idx.numel()
     _need(idx, "idx", torch.int32)
     is_bf16 = _act(a, "a")
@@ -801,6 +807,10 @@ def moe_rows(a, w, idx, out, mode: str) -> None:
         top = idx.shape[1]
         n_out, code, a_div = r // 2, 0, top
         if a.shape != (idx.shape[0], k) or r % 2:
+            raise KernelError(f"moe_rows: activations {tuple(a.shape)} against weights {tuple(w.shape)}")
+    elif mode == "up_relu2":
+        n_out, code, a_div = r, 2, idx.shape[1]
+        if a.shape != (idx.shape[0], k):
             raise KernelError(f"moe_rows: activations {tuple(a.shape)} against weights {tuple(w.shape)}")
     elif mode == "down":
         n_out, code, a_div = r, 1, 1
@@ -898,7 +908,7 @@ def moe_grouped_lib() -> ctypes.CDLL:
                 if os.environ.get(var):
                     defs[name] = int(os.environ[var])
             lib = _load(build.build_library("moe_grouped", ("moe_grouped.cu",), defs))
-            lib.dryft_moe_grouped.argtypes = [_p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p, _p, _p]
+            lib.dryft_moe_grouped.argtypes = [_p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p, _p, _i, _p]
             lib.dryft_moe_grouped.restype = _i
             lib.dryft_moe_grouped_work_ints.argtypes = [_i, _i]
             lib.dryft_moe_grouped_work_ints.restype = _ll
@@ -906,16 +916,17 @@ def moe_grouped_lib() -> ctypes.CDLL:
         return _moe_grouped
 
 
-def moe_grouped(h, w_gate_up, w_down, idx, y) -> None:
+def moe_grouped(h, w_gate_up, w_down, idx, y, gated: bool = True) -> None:
     """``y[n*top + k] = expert idx[n, k] applied to h[n]`` (bfloat16) with the assignments sorted by expert on the device and
-    both expert products as grouped tensor-core products (``csrc/moe_grouped.cu``: three launches, no host round trip)."""
+    both expert products as grouped tensor-core products (``csrc/moe_grouped.cu``: three launches, no host round trip).
+    ``gated=False``: ``w_gate_up`` is ``[E, F, W]`` (no gate rows) and the activation is ``max(., 0)^2``."""
     n, width = h.shape
     top = idx.shape[1]
     e, two_f, _ = w_gate_up.shape
-    f = two_f // 2
+    f = two_f // 2 if gated else two_f
     _need(h, "h", torch.bfloat16)
     _need(idx, "idx", torch.int32, (n, top))
-    _need(w_gate_up, "w_gate_up", torch.bfloat16, (e, 2 * f, width))
+    _need(w_gate_up, "w_gate_up", torch.bfloat16, (e, (2 if gated else 1) * f, width))
     _need(w_down, "w_down", torch.bfloat16, (e, width, f))
     _need(y, "y", torch.bfloat16, (n * top, width))
     if not moe_grouped_supported(width, f):
@@ -924,7 +935,7 @@ def moe_grouped(h, w_gate_up, w_down, idx, y) -> None:
     work = torch.empty(int(lib.dryft_moe_grouped_work_ints(n * top, e)), dtype=torch.int32, device=h.device)
     act = torch.empty((n * top, f), dtype=torch.bfloat16, device=h.device)
     _ok(lib.dryft_moe_grouped(_ptr(h), _ptr(w_gate_up), _ptr(w_down), _ptr(idx), n, top, e, width, f, _ptr(act), _ptr(y), _ptr(work),
-                              _stream()), f"moe_grouped ({e} experts, {width} x {f})", n_kernels=3)
+                              int(gated), _stream()), f"moe_grouped ({e} experts, {width} x {f})", n_kernels=3)
 
 
 # ----------------------------------------------------------------------------- matrix products
@@ -1562,3 +1573,242 @@ def latent_unfold_o(o_lat, w_v, gate, gate_col: int, out) -> None:
         gate_ptr, gate_ld = ctypes.c_void_p(gate.data_ptr() + gate_col * gate.element_size()), gate.shape[1]
     _ok(latent_attn_lib().dryft_latent_unfold_o(_act(out, "out"), _ptr(o_lat), _ptr(w_v), gate_ptr, gate_ld, _ptr(out), n, n_heads, kv_rank,
                                                 vdim, _stream()), "latent_unfold_o")
+
+
+# ----------------------------------------------------------------------------- a stream whose norm follows the sum
+def rowops_lib() -> ctypes.CDLL:
+    """Row-wise kernels around a 32-bit stream with the norm after the sum, and activations over whole rows."""
+    return _single_lib("rowops", {
+        "dryft_gated_postnorm": [_i, _p, _p, _i, _p, _p, _i, _p, _i, _p, _p, _f, _f, _p, _p, _i, _i, _p],
+        "dryft_polynorm": [_i, _p, _i, _p, _f, _p, _i, _i, _p],
+        "dryft_relu2": [_i, _p, _i, _p, _i, _i, _p],
+        "dryft_gated_group_norm": [_i, _p, _p, _i, _p, _i, _f, _p, _i, _i, _p],
+    })
+
+
+def gated_postnorm(y, x32, norm_w, alpha: float, eps: float, h=None, *, gate=None, gate_b=None, wts=None, top: int = 0,
+                   shared=None, shared_gate=None) -> None:
+    """``v = alpha * x32 + g * (y [+ sigmoid(shared_gate) * shared])`` with ``g = sigmoid(gate + gate_b)`` (1 without a gate);
+    ``x32 <- v / sqrt(mean(v^2) + eps) * norm_w`` in place and ``h <- x32`` in the activation type (if given).  With ``wts
+    [n, top]``, ``y`` holds ``top`` rows per row of the stream and their weighted sum is formed first.  ``gate`` and
+    ``shared_gate`` may be column slices of a product's output (rows ``gate.stride(0)`` apart)."""
+    n, w = x32.shape
+    _need(x32, "x32", torch.float32)
+    _need(norm_w, "norm_w", torch.float32, (w,))
+    is_bf16 = _act(y, "y")
+    _need(y, "y", None, (n * top if top else n, w))
+    if top:
+        _need(wts, "wts", torch.float32, (n, top))
+    if h is not None:
+        _need(h, "h", y.dtype, (n, w))
+    gl_ld = 0
+    if gate is not None:
+        if gate.dtype != y.dtype or gate.shape != (n, w) or gate.stride(1) != 1 or not gate.is_cuda:
+            raise KernelError(f"gated_postnorm: gate logits {tuple(gate.shape)} {gate.dtype} against a stream {tuple(x32.shape)}")
+        gl_ld = gate.stride(0)
+        _need(gate_b, "gate_b", torch.float32, (w,))
+    sg_ld = 0
+    if shared is not None:
+        _need(shared, "shared", y.dtype, (n, w))
+        if shared_gate is not None:
+            if shared_gate.dtype != y.dtype or shared_gate.shape[0] != n or not shared_gate.is_cuda:
+                raise KernelError("gated_postnorm: the always-on expert's gate logits are one per token, in the activation type")
+            sg_ld = shared_gate.stride(0)
+    _ok(rowops_lib().dryft_gated_postnorm(is_bf16, _ptr(y), _ptr(wts if top else None), int(top), _ptr(shared), _ptr(shared_gate),
+                                          sg_ld, _ptr(gate), gl_ld, _ptr(gate_b), _ptr(norm_w), float(alpha), float(eps), _ptr(x32),
+                                          _ptr(h), n, w, _stream()), f"gated_postnorm (width {w})")
+
+
+def polynorm(z, coef, eps: float, out) -> None:
+    """``out = a N(z) + b N(z^2) + c N(z^3) + e`` over each row, ``N(u) = u / sqrt(mean(u^2) + eps)``, ``coef = [a, b, c, e]``."""
+    n, f = z.shape
+    if z.stride(1) != 1 or not z.is_cuda:
+        raise KernelError("polynorm: rows must be contiguous and on the device")
+    _need(coef, "coef", torch.float32, (4,))
+    _need(out, "out", z.dtype, (n, f))
+    _ok(rowops_lib().dryft_polynorm(_act(z, "z"), _ptr(z), z.stride(0), _ptr(coef), float(eps), _ptr(out), n, f, _stream()),
+        f"polynorm ({f} values a row)")
+
+
+def relu2(z, out) -> None:
+    """``out = max(z, 0)^2``; ``z`` may be a column slice of a product's output."""
+    n, f = out.shape
+    if z.shape != (n, f) or z.stride(1) != 1 or not z.is_cuda or z.dtype != out.dtype:
+        raise KernelError(f"relu2: input {tuple(z.shape)} {z.dtype} against output {tuple(out.shape)} {out.dtype}")
+    _need(out, "out")
+    _ok(rowops_lib().dryft_relu2(_act(z, "z"), _ptr(z), z.stride(0), _ptr(out), n, f, _stream()), "relu2")
+
+
+def gated_group_norm(y, z, weight, parts: int, eps: float, out) -> None:
+    """``v = y * silu(z)``; each of ``parts`` equal parts of a row divided by its own root mean square, times ``weight``.
+    ``y [n, inner]`` float32, ``z`` float32 (a column slice is fine), ``out [n, inner]`` in the activation type."""
+    n, inner = y.shape
+    _need(y, "y", torch.float32)
+    if z.dtype != torch.float32 or z.shape != (n, inner) or z.stride(1) != 1 or not z.is_cuda:
+        raise KernelError(f"gated_group_norm: gate {tuple(z.shape)} {z.dtype} against {tuple(y.shape)}")
+    _need(weight, "weight", torch.float32, (inner,))
+    _need(out, "out", None, (n, inner))
+    _ok(rowops_lib().dryft_gated_group_norm(_act(out, "out"), _ptr(y), _ptr(z), z.stride(0), _ptr(weight), int(parts), float(eps),
+                                            _ptr(out), n, inner, _stream()), f"gated_group_norm ({inner} in {parts} parts)")
+
+
+# ----------------------------------------------------------------------------- selective state-space mixer
+SSM_MAX_STATE = 256    # state rows a head may have (a lane of the scan holds up to eight)
+SSM_MAX_TAPS = 16
+
+
+def ssm_lib() -> ctypes.CDLL:
+    return _single_lib("ssm", {
+        "dryft_ssm_conv": [_p, _i, _i, _i, _p, _p, _i, _p, _p, _i, _p, _p, _i, _p],
+        "dryft_ssm_scan": [_p, _i, _p, _i, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p, _p],
+    })
+
+
+def ssm_conv(proj, x_off: int, conv_w, conv_b, cu_q, seq_slot, n_seqs: int, tail, out) -> None:
+    """``out[t, c] = silu(conv_b[c] + sum_j conv_w[c, j] * in[t - (taps-1) + j, c])`` over the ``C`` channels of ``proj [n, ld]``
+    (float32) from column ``x_off``; inputs from before the step come from ``tail [slots, taps-1, C]``, which is then
+    advanced.  Two launches (one when there is a single tap)."""
+    n, ld = proj.shape
+    c, taps = conv_w.shape
+    _need(proj, "proj", torch.float32)
+    _need(conv_w, "conv_w", torch.float32)
+    _need(conv_b, "conv_b", torch.float32, (c,))
+    _need(out, "out", torch.float32, (n, c))
+    if x_off < 0 or x_off + c > ld:
+        raise KernelError(f"ssm_conv: {c} channels from column {x_off} of a row of {ld}")
+    if taps > 1:
+        _need(tail, "tail", torch.float32, (None, taps - 1, c))
+    for t, nm in ((cu_q, "cu_q"), (seq_slot, "seq_slot")):
+        _need(t, nm, torch.int32)
+    _ok(ssm_lib().dryft_ssm_conv(_ptr(proj), ld, int(x_off), c, _ptr(cu_q), _ptr(seq_slot), int(n_seqs), _ptr(conv_w), _ptr(conv_b),
+                                 taps, _ptr(tail if taps > 1 else None), _ptr(out), n, _stream()),
+        f"ssm_conv ({c} channels, {taps} taps)", n_kernels=2 if taps > 1 else 1)
+
+
+def ssm_scan(xbc, proj, dt_off: int, dt_bias, a_log, d_skip, cu_q, seq_slot, n_seqs: int, heads: int, groups: int, n_state: int,
+             vdim: int, state, y) -> None:
+    """The recurrence ``S_t = exp(-exp(a_log) dt_t) S_(t-1) + dt_t B_t x_t^T``, ``y_t = S_t^T C_t + D x_t`` per head, with
+    ``dt_t = softplus(proj[t, dt_off + head] + dt_bias)``; ``xbc [n, heads*vdim + 2*groups*n_state]`` holds x, B, C after
+    the convolution; ``state [slots, heads, n_state, vdim]`` float32 is read and left advanced; ``y [n, heads*vdim]``."""
+    n, ch = xbc.shape
+    inner = heads * vdim
+    _need(xbc, "xbc", torch.float32, (n, inner + 2 * groups * n_state))
+    _need(proj, "proj", torch.float32, (n, None))
+    for t, nm in ((dt_bias, "dt_bias"), (a_log, "a_log"), (d_skip, "d_skip")):
+        _need(t, nm, torch.float32, (heads,))
+    _need(state, "state", torch.float32, (None, heads, n_state, vdim))
+    _need(y, "y", torch.float32, (n, inner))
+    for t, nm in ((cu_q, "cu_q"), (seq_slot, "seq_slot")):
+        _need(t, nm, torch.int32)
+    if dt_off < 0 or dt_off + heads > proj.shape[1]:
+        raise KernelError(f"ssm_scan: {heads} step sizes from column {dt_off} of a row of {proj.shape[1]}")
+    _ok(ssm_lib().dryft_ssm_scan(_ptr(xbc), ch, _ptr(proj), proj.shape[1], int(dt_off), _ptr(dt_bias), _ptr(a_log), _ptr(d_skip),
+                                 _ptr(cu_q), _ptr(seq_slot), int(n_seqs), heads, groups, n_state, vdim, _ptr(state), _ptr(y),
+                                 _stream()), f"ssm_scan ({heads} heads, state {n_state} x {vdim})")
+
+
+# ----------------------------------------------------------------------------- windowed attention with pooled blocks and a sink
+def pool_attention_lib(qk_dim: int, v_dim: int, group: int) -> ctypes.CDLL:
+    if qk_dim <= 0 or v_dim <= 0 or qk_dim > 512 or v_dim > 512:
+        raise KernelError(f"pooled-window attention takes key and value sizes up to 512, got {qk_dim}, {v_dim}")
+    if group < 1 or group > 16:
+        raise KernelError(f"pooled-window attention takes 1..16 query heads per kv head, got {group}")
+    key = ("pool_attn", qk_dim, v_dim, group)
+    with _lock:
+        lib = _variants.get(key)
+        if lib is None:
+            path = build.build_library("pool_attn", ("pool_attn.cu",),
+                                       {"DRYFT_QK_DIM": qk_dim, "DRYFT_V_DIM": v_dim, "DRYFT_GROUP": group})
+            lib = _load(path)
+            lib.dryft_pool_attn_prep.argtypes = [_i, _p, _i, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f,
+                                                 _i, _p]
+            lib.dryft_pool_attn_blocks.argtypes = [_i, _p, _p, _p, _i, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _p]
+            lib.dryft_pool_attn_rows.argtypes = [_i, _p, _p, _p, _p, _i, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _f,
+                                                 _i, _i, _p]
+            for fn in ("dryft_pool_attn_prep", "dryft_pool_attn_blocks", "dryft_pool_attn_rows"):
+                getattr(lib, fn).restype = _i
+            if (lib.dryft_pool_attn_qk_dim(), lib.dryft_pool_attn_v_dim(), lib.dryft_pool_attn_group()) != (qk_dim, v_dim, group):
+                raise KernelError(f"{path} was compiled for other sizes")
+            _variants[key] = lib
+        return lib
+
+
+def pool_attention_prefill_supported(qk_dim: int, v_dim: int, group: int) -> bool:
+    """Whether the tensor-core prompt kernel of the pooled-window attention takes this head shape."""
+    return False
+
+
+def pool_attn_prep(proj, q_bias, k_bias, v_bias, inv_freq, inv_freq_lo, rot: int, tok_slot, tok_pos, q_out, k_pages, v_pages,
+                   page_table, n_heads: int, n_kv: int, eps: float, write_kv: bool) -> None:
+    """Per token of ``proj [n, H*D (+ G*D + G*DV)]``: bias, rotation of the first ``rot`` dims (rotate-half), division by the
+    root mean square over the head (no weight; ``eps < 0``: not divided) for q and k; v plus its bias; k and v into the cache
+    pages."""
+    n, ld = proj.shape
+    d, dv = q_out.shape[2], v_pages.shape[-1]
+    _need(proj, "proj")
+    _need(q_out, "q_out", proj.dtype, (n, n_heads, d))
+    _need(k_pages, "k_pages", proj.dtype, (None, n_kv, None, d))
+    _need(v_pages, "v_pages", proj.dtype, (None, n_kv, k_pages.shape[2], dv))
+    _need(page_table, "page_table", torch.int32)
+    if ld < n_heads * d + (n_kv * (d + dv) if write_kv else 0):
+        raise KernelError(f"pool_attn_prep: a row of {ld} values is too short for {n_heads} + {n_kv} heads")
+    for t, nm, cnt in ((q_bias, "q_bias", n_heads * d), (k_bias, "k_bias", n_kv * d), (v_bias, "v_bias", n_kv * dv)):
+        if t is not None:
+            _need(t, nm, torch.float32, (cnt,))
+    if rot:
+        _need(inv_freq, "inv_freq", torch.float32, (rot // 2,))
+        if inv_freq_lo is not None:
+            _need(inv_freq_lo, "inv_freq_lo", torch.float32, (rot // 2,))
+    lib = pool_attention_lib(d, dv, n_heads // n_kv)
+    _ok(lib.dryft_pool_attn_prep(_act(proj, "proj"), _ptr(proj), ld, _ptr(q_bias), _ptr(k_bias), _ptr(v_bias), _ptr(inv_freq),
+                                 _ptr(inv_freq_lo), int(rot), _ptr(tok_slot), _ptr(tok_pos), _ptr(q_out), _ptr(k_pages), _ptr(v_pages),
+                                 _ptr(page_table), page_table.shape[1], k_pages.shape[2], n, n_heads, n_kv, float(eps),
+                                 int(write_kv), _stream()), f"pool_attn_prep ({n_heads}/{n_kv} heads of {d})")
+
+
+def pool_attn_blocks(k_pages, v_pages, page_table, pk_pages, pv_pages, pool_table, tok_slot, tok_pos, n: int, pool: int,
+                     group: int) -> None:
+    """Every token of the step that completes a block of ``pool`` positions leaves the means of the block's cached keys and
+    values in the pooled pages."""
+    n_kv, page, d = k_pages.shape[1], k_pages.shape[2], k_pages.shape[3]
+    dv = v_pages.shape[-1]
+    _need(k_pages, "k_pages")
+    _need(v_pages, "v_pages", k_pages.dtype)
+    _need(pk_pages, "pk_pages", k_pages.dtype, (None, n_kv, page, d))
+    _need(pv_pages, "pv_pages", k_pages.dtype, (None, n_kv, page, dv))
+    _need(pool_table, "pool_table", torch.int32)
+    lib = pool_attention_lib(d, dv, group)
+    _ok(lib.dryft_pool_attn_blocks(_act(k_pages, "k_pages"), _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.shape[1], page,
+                                   _ptr(pk_pages), _ptr(pv_pages), _ptr(pool_table), pool_table.shape[1], _ptr(tok_slot), _ptr(tok_pos),
+                                   n, n_kv, int(pool), _stream()), f"pool_attn_blocks (blocks of {pool})")
+
+
+def pool_attn_rows(q, k_pages, v_pages, page_table, pooled, sink, tok_slot, tok_pos, out, scale: float, size: int, pool: int,
+                   n_splits: int = 1, part_o=None, part_ml=None) -> None:
+    """Row-wise attention of ``q [n, H, D]`` over the last ``size`` cached tokens and, beside them, the pooled row of every block
+    of ``pool`` positions that lies wholly before them (``pooled = (pk_pages, pv_pages, pool_table)``; ``pool = 0``: none), one
+    softmax whose denominator also holds ``exp(sink[head])`` (if given).  ``out [n, H, DV]``."""
+    n, n_heads, d = q.shape
+    n_kv, page = k_pages.shape[1], k_pages.shape[2]
+    dv = v_pages.shape[-1]
+    _need(q, "q")
+    _need(k_pages, "k_pages", q.dtype, (None, n_kv, page, d))
+    _need(v_pages, "v_pages", q.dtype, (None, n_kv, page, dv))
+    _need(out, "out", q.dtype, (n, n_heads, dv))
+    if sink is not None:
+        _need(sink, "sink", torch.float32, (n_heads,))
+    pk = pv = pt = None
+    if pool:
+        pk, pv, pt = pooled
+        _need(pk, "pk_pages", q.dtype, (None, n_kv, page, d))
+        _need(pv, "pv_pages", q.dtype, (None, n_kv, page, dv))
+        _need(pt, "pool_table", torch.int32)
+    if n_splits > 1:
+        _need(part_o, "part_o", torch.float32, (n, n_heads, n_splits, dv))
+        _need(part_ml, "part_ml", torch.float32, (n, n_heads, n_splits, 2))
+    lib = pool_attention_lib(d, dv, n_heads // n_kv)
+    _ok(lib.dryft_pool_attn_rows(_act(q, "q"), _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.shape[1], page,
+                                 _ptr(pk), _ptr(pv), _ptr(pt), pt.shape[1] if pt is not None else 0, _ptr(sink), _ptr(tok_slot),
+                                 _ptr(tok_pos), _ptr(out), _ptr(part_o), _ptr(part_ml), n, n_kv, int(n_splits), float(scale), int(size),
+                                 int(pool), _stream()), f"pool_attn_rows (window {size}, blocks of {pool})",
+        n_kernels=2 if n_splits > 1 else 1)

@@ -14,13 +14,13 @@ folded into the matrix products instead (``csrc/gemm_small_m.cu``).
 
 from __future__ import annotations
 
-from typing import Optional, Tuple
+from typing import Dict, Mapping, Optional, Tuple
 
 import torch
 
 from ..ops import kernels as K
-from .base import Residual, StepContext, fused_rms, register_block
-from .linear import weighted_for
+from .base import Residual, Runtime, StepContext, TensorInfo, fused_rms, register_block, register_connection
+from .linear import linear, weighted_for
 
 
 @register_block("prenorm")
@@ -120,4 +120,80 @@ class OutNormBlock:
             h = self.norm_ffn.add_into(x, y, wts=wts, top=top)
         else:
             h = self.norm_ffn.add_into(x, self.ffn.forward(h, ctx))
+        return Residual(x, h=h)
+
+
+@register_connection("gated_sum")
+class GatedSum:
+    """How a sublayer's result ``y`` joins a stream whose norm follows the sum: ``keep * x + g * y`` with ``g = sigmoid(W h +
+    b)`` element by element, ``h`` being the sublayer's own input.  ``params``: ``size``, ``keep`` (default 1), ``gate`` and
+    ``gate_bias`` (tensor names behind the prefix; no ``gate``: ``g = 1`` and no tensors)."""
+
+    @staticmethod
+    def tensors(params: Mapping, prefix: str) -> Dict[str, TensorInfo]:
+        if not params.get("gate"):
+            return {}
+        t = {prefix + params["gate"]: TensorInfo((params["size"], params["size"]), "matrix")}
+        if params.get("gate_bias"):
+            t[prefix + params["gate_bias"]] = TensorInfo((params["size"],), "vector", False, 0.0)
+        return t
+
+    def __init__(self, params: Mapping, prefix: str, weights, rt: Runtime):
+        self.rt = rt
+        self.keep = float(params.get("keep", 1.0))
+        self.w = weights.load(prefix + params["gate"], "matrix") if params.get("gate") else None
+        self.b = weights.load(prefix + params["gate_bias"], "vector") if self.w is not None and params.get("gate_bias") else None
+
+    def logits(self, h: torch.Tensor) -> Optional[torch.Tensor]:
+        """``W h`` in the activation type (the bias and the sigmoid belong to the kernel that forms the sum)."""
+        return linear(h, self.w, self.rt) if self.w is not None else None
+
+
+@register_block("postnorm")
+class PostNormBlock:
+    """The norm after the sum, around a 32-bit stream:
+
+        x <- norm_mixer(keep * x + g1 * mixer(h))      h = x rounded to the activation type (the sublayers read the stream itself)
+        x <- norm_ffn  (keep * x + g2 * ffn(h))
+
+    ``extra`` holds a ``gated_sum`` connection per sublayer (``gate_mixer``, ``gate_ffn``) that gives ``keep`` and the gate
+    ``g``; each sum, gate and norm is one kernel that also leaves the rounded stream for the next sublayer
+    (``csrc/rowops.cu``).  The norms must offer ``sum_norm``.  A routed feed-forward (``forward_parts``) has its weighted
+    sum, and its always-on expert (``forward_shared``), joined inside that kernel.  A layer without a feed-forward stops
+    after the mixer."""
+
+    def __init__(self, norm_mixer, mixer, norm_ffn, ffn, extra: Optional[Mapping] = None):
+        extra = extra or {}
+        for nm in (norm_mixer, norm_ffn):
+            if nm is not None and not hasattr(nm, "sum_norm"):
+                raise ValueError("the 'postnorm' arrangement needs norms that offer sum_norm (a 32-bit stream)")
+        self.norm_mixer, self.mixer, self.norm_ffn, self.ffn = norm_mixer, mixer, norm_ffn, ffn
+        self.gate_mixer, self.gate_ffn = extra.get("gate_mixer"), extra.get("gate_ffn")
+        if self.gate_mixer is None or (ffn is not None and self.gate_ffn is None):
+            raise ValueError("the 'postnorm' arrangement needs a connection per sublayer (extra parts gate_mixer, gate_ffn)")
+        self.extra = dict(extra)
+
+    def forward(self, res: Residual, ctx: StepContext, cache, state, owns_cache: bool = True) -> Residual:
+        x = res.x
+        if x.dtype != torch.float32:
+            raise ValueError("the 'postnorm' arrangement keeps its stream in float32; the embedding must start one")
+        if res.delta is not None:
+            x.add_(res.delta)
+        act = self.mixer.rt.dtype
+        h = res.h if res.h is not None else (x if act == torch.float32 else x.to(act))
+        conn = self.gate_mixer
+        a = self.mixer.forward(h, ctx, cache, state, owns_cache)
+        h = self.norm_mixer.sum_norm(x, a, conn.keep, gate=conn.logits(h), gate_bias=conn.b)
+        if self.ffn is None:
+            return Residual(x, h=h)
+        conn = self.gate_ffn
+        gl = conn.logits(h)
+        parts = getattr(self.ffn, "forward_parts", None)
+        if parts is not None:
+            y, wts, top = parts(h, ctx)
+            sh = self.ffn.forward_shared(h) if hasattr(self.ffn, "forward_shared") else None
+            ys, sg = sh if sh is not None else (None, None)
+            h = self.norm_ffn.sum_norm(x, y, conn.keep, gate=gl, gate_bias=conn.b, wts=wts, top=top, shared=ys, shared_gate=sg)
+        else:
+            h = self.norm_ffn.sum_norm(x, self.ffn.forward(h, ctx), conn.keep, gate=gl, gate_bias=conn.b)
         return Residual(x, h=h)

@@ -18,25 +18,32 @@ from .linear import fusable_rows, linear
 
 @register_embedding("embedding")
 class Embedding:
+    """``params["name"]``: the table's tensor name behind the prefix (default ``weight``).  ``params["stream32"]``: the rows
+    start a 32-bit residual stream (a ``Residual`` whose ``x`` is float32 and whose ``h`` is the rows in the activation type)."""
+
     @staticmethod
     def tensors(params: Mapping, prefix: str) -> Dict[str, TensorInfo]:
-        return {prefix + "weight": TensorInfo((params["vocab_size"], params["hidden_size"]), "table")}
+        return {prefix + params.get("name", "weight"): TensorInfo((params["vocab_size"], params["hidden_size"]), "table")}
 
     def __init__(self, params: Mapping, prefix: str, weights, rt: Runtime):
         self.rt = rt
         self.vocab = int(params["vocab_size"])
         self.hidden = int(params["hidden_size"])
-        self.table = weights.load(prefix + "weight", "table")
+        self.table = weights.load(prefix + params.get("name", "weight"), "table")
+        self.stream32 = bool(params.get("stream32", False))
         # raised by the gather for an id outside the table (its row is zeroed, not read); read with the other
         # device flags by ``kernels.check_error_flags``
         self.err = torch.zeros(1, dtype=torch.int32, device=rt.device)
         K.watch_flag(self.err, "a token id outside the embedding table reached the embedding gather (its row was zeroed)")
 
-    def forward(self, tokens: torch.Tensor, n_rows: int) -> torch.Tensor:
+    def forward(self, tokens: torch.Tensor, n_rows: int):
         out = torch.empty((n_rows, self.hidden), dtype=self.table.dtype, device=self.table.device)
         K.embed(tokens, self.table, out, self.err)
         # a table the checkpoint stores in 32-bit stays 32-bit; its rows are rounded on the way out
-        return out if out.dtype == self.rt.dtype else out.to(self.rt.dtype)
+        h = out if out.dtype == self.rt.dtype else out.to(self.rt.dtype)
+        if self.stream32:
+            return Residual(out if out.dtype == torch.float32 else out.to(torch.float32), h=h)
+        return h
 
 
 @register_embedding("sinusoid_embedding")

@@ -126,3 +126,50 @@ class ClampedGLU:
         for r0 in range(0, n, chunk):
             out[r0:r0 + chunk] = self._rows(h[r0:r0 + chunk])
         return out
+
+
+@register_ffn("polynorm_mlp")
+class PolyNormMLP:
+    """``down(act(up(h)))`` without a gate branch, ``act(z) = a N(z) + b N(z^2) + c N(z^3) + e``: powers element by element,
+    ``N`` the division of a token's whole vector of feed-forward values by its root mean square (``eps`` inside the root),
+    the four numbers a tensor of the layer.  The norms' sums are 32-bit (``csrc/rowops.cu:polynorm``).
+    ``params["names"]`` maps ``up``, ``down``, ``act`` to the tensors' names behind the prefix."""
+
+    @staticmethod
+    def _names(params: Mapping, prefix: str) -> Dict[str, str]:
+        given = params.get("names") or {}
+        return {r: prefix + given.get(r, d) for r, d in (("up", "up_proj.weight"), ("down", "down_proj.weight"), ("act", "act.weight"))}
+
+    @staticmethod
+    def tensors(params: Mapping, prefix: str) -> Dict[str, TensorInfo]:
+        h, i = params["hidden_size"], params["intermediate_size"]
+        nm = PolyNormMLP._names(params, prefix)
+        # the four numbers are drawn around 1/3 so that random weights give an activation of ordinary size
+        return {nm["up"]: TensorInfo((i, h), "matrix"), nm["down"]: TensorInfo((h, i), "matrix"),
+                nm["act"]: TensorInfo((4,), "vector", False, 1.0 / 3.0)}
+
+    def __init__(self, params: Mapping, prefix: str, weights, rt: Runtime):
+        self.rt = rt
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.eps = float(params["eps"])
+        nm = self._names(params, prefix)
+        self.w_up = weights.load(nm["up"], "matrix")
+        self.w_down = weights.load(nm["down"], "matrix")
+        self.coef = weights.load(nm["act"], "vector")   # float32 [4]
+
+    def _rows(self, h: torch.Tensor) -> torch.Tensor:
+        z = linear(h, self.w_up, self.rt)
+        act = torch.empty_like(z)
+        K.polynorm(z, self.coef, self.eps, act)
+        return linear(act, self.w_down, self.rt)
+
+    def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        n = h.shape[0]
+        chunk = self.rt.ffn_chunk_rows
+        if n <= chunk:
+            return self._rows(h)
+        out = torch.empty((n, self.hidden), dtype=h.dtype, device=h.device)
+        for r0 in range(0, n, chunk):
+            out[r0:r0 + chunk] = self._rows(h[r0:r0 + chunk])
+        return out

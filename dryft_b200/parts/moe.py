@@ -1,6 +1,10 @@
 """Mixture-of-experts feed-forward with group-limited top-k routing.
 
-``E`` small SwiGLU experts (``down(silu(gate(h)) * up(h))``, no biases); a token uses ``top`` of them.  Router:
+``E`` small experts without biases -- SwiGLU (``down(silu(gate(h)) * up(h))``) or, with ``activation="relu2"``, ungated
+(``down(max(up(h), 0)^2)``) -- of which a token uses ``top``.  The router may have a bias on its logits (``router_bias``: a
+tensor name), and ``renormalize`` divides the chosen scores by their sum, which is the softmax over the chosen logits only.
+An always-on expert of the same form (``shared``: ``{"intermediate_size", "gate"}``) may run for every token beside them; its
+output is weighted by ``sigmoid(w_gate . h)``, one number per token, when it has a gate.  Router:
 ``z = W_router h`` and ``s = softmax(z)`` over all experts in 32-bit; expert ``e`` belongs to group ``e // (E / groups)`` (contiguous and equally
 sized), a group is ranked by the maximum of its members' scores, and selection is restricted to the ``keep`` highest-ranked
 groups; within them the ``top`` largest scores name the token's experts, each weighted by its own score ``s`` with no
@@ -24,8 +28,9 @@ from ..ops import kernels as K
 from .base import Runtime, StepContext, TensorInfo, register_ffn
 from .linear import linear
 
-_ROLES = {"router": "router.weight", "expert": "experts.{}.", "gate": "gate_proj.weight", "up": "up_proj.weight",
-          "down": "down_proj.weight"}
+_ROLES = {"router": "router.weight", "router_bias": "router.bias", "expert": "experts.{}.", "gate": "gate_proj.weight",
+          "up": "up_proj.weight", "down": "down_proj.weight", "shared": "shared.", "shared_gate": "shared.gate.weight"}
+SHARED_PAD = 8   # the always-on expert's first product carries its gate logit as one more column, padded to this many
 
 
 def _names(params: Mapping) -> Dict[str, str]:
@@ -39,12 +44,25 @@ class MoE:
     def tensors(params: Mapping, prefix: str) -> Dict[str, TensorInfo]:
         w, f, e = params["hidden_size"], params["intermediate_size"], params["experts"]
         nm = _names(params)
+        gated = params.get("activation", "swiglu") == "swiglu"
         t = {prefix + nm["router"]: TensorInfo((e, w), "matrix")}
+        if params.get("router_bias"):
+            t[prefix + nm["router_bias"]] = TensorInfo((e,), "vector", False, 0.0)
         for i in range(e):
             ep = prefix + nm["expert"].format(i)
-            t[ep + nm["gate"]] = TensorInfo((f, w), "matrix")
+            if gated:
+                t[ep + nm["gate"]] = TensorInfo((f, w), "matrix")
             t[ep + nm["up"]] = TensorInfo((f, w), "matrix")
             t[ep + nm["down"]] = TensorInfo((w, f), "matrix")
+        sh = params.get("shared")
+        if sh is not None:
+            fs, sp = sh["intermediate_size"], prefix + nm["shared"]
+            if gated:
+                t[sp + nm["gate"]] = TensorInfo((fs, w), "matrix")
+            t[sp + nm["up"]] = TensorInfo((fs, w), "matrix")
+            t[sp + nm["down"]] = TensorInfo((w, fs), "matrix")
+            if sh.get("gate", True):
+                t[prefix + nm["shared_gate"]] = TensorInfo((1, w), "matrix")
         return t
 
     def __init__(self, params: Mapping, prefix: str, weights, rt: Runtime):
@@ -58,23 +76,46 @@ class MoE:
         self.renorm = bool(params.get("renormalize", False))
         if self.experts % self.groups or not 1 <= self.keep <= self.groups or not 1 <= self.top <= self.experts:
             raise ValueError(f"moe: {self.experts} experts, {self.groups} groups, keep {self.keep}, top {self.top} do not go together")
+        act = params.get("activation", "swiglu")
+        if act not in ("swiglu", "relu2"):
+            raise ValueError(f"moe: activation must be 'swiglu' or 'relu2', got {act!r}")
+        self.gated = act == "swiglu"
         nm = _names(params)
         # The router's logits are 32-bit sums.  In the bfloat16 path its operands are the bfloat16 activations and the
         # weight as stored (their products are exact in 32-bit), multiplied by the tensor-core products with 32-bit
         # accumulation and a 32-bit result; in the 32-bit path everything is float32.
         self.w_router = weights.load(prefix + nm["router"], "matrix")
+        self.router_bias = weights.load(prefix + nm["router_bias"], "vector") if params.get("router_bias") else None
         gu, dn = [], []
         for i in range(self.experts):
             ep = prefix + nm["expert"].format(i)
-            gu += [ep + nm["gate"], ep + nm["up"]]
+            gu += [ep + nm["gate"], ep + nm["up"]] if self.gated else [ep + nm["up"]]
             dn.append(ep + nm["down"])
-        # [E, 2F, W] (an expert's gate rows, then its up rows) and [E, W, F]
-        self.w_gate_up = weights.load_fused(gu, [self.inter] * len(gu), self.hidden).view(self.experts, 2 * self.inter, self.hidden)
+        # [E, 2F, W] (an expert's gate rows, then its up rows; [E, F, W] without a gate) and [E, W, F]
+        self.w_gate_up = weights.load_fused(gu, [self.inter] * len(gu), self.hidden).view(
+            self.experts, (2 if self.gated else 1) * self.inter, self.hidden)
         self.w_down = weights.load_fused(dn, [self.hidden] * len(dn), self.inter).view(self.experts, self.hidden, self.inter)
         self.use_grouped = (rt.is_bf16 and self.w_gate_up.dtype == torch.bfloat16
                             and K.moe_grouped_supported(self.hidden, self.inter))
         if self.use_grouped:
             K.moe_grouped_lib()
+        # the always-on expert: its first product also yields the per-token gate logit (one more row of the weight, padded)
+        self.shared_inter = 0
+        sh = params.get("shared")
+        if sh is not None:
+            if self.gated:
+                raise ValueError("moe: an always-on expert is served for ungated experts (activation 'relu2') only")
+            self.shared_inter = fs = int(sh["intermediate_size"])
+            self.shared_gate = bool(sh.get("gate", True))
+            sp = prefix + nm["shared"]
+            names, rows = [sp + nm["up"]], [fs]
+            if self.shared_gate:
+                names.append(prefix + nm["shared_gate"])
+                rows.append(1)
+            w = weights.load_fused(names, rows, self.hidden)
+            pad = (-w.shape[0]) % SHARED_PAD
+            self.w_shared_up = torch.cat([w, torch.zeros((pad, self.hidden), dtype=w.dtype, device=w.device)]) if pad else w
+            self.w_shared_down = weights.load(sp + nm["down"], "matrix")
 
     GROUPED_MIN_TOKENS = 32   # below this every assignment streams its expert's weights itself
     ROUTE_ROWS_MAX = 16       # up to this many tokens the router's product and choice are one launch ...
@@ -88,11 +129,23 @@ class MoE:
         wts = torch.empty((n, self.top), dtype=torch.float32, device=h.device)
         if (n <= self.ROUTE_ROWS_MAX and self.w_router.dtype == h.dtype and self.w_router.numel() <= self.ROUTE_ROWS_MAX_WEIGHTS
                 and K.moe_route_rows_supported(self.hidden, self.experts, self.groups, h.element_size())):
-            K.moe_route_rows(h, self.w_router, self.groups, self.keep, self.top, idx, wts, renorm=self.renorm)   # one launch
+            K.moe_route_rows(h, self.w_router, self.groups, self.keep, self.top, idx, wts, renorm=self.renorm,
+                             bias=self.router_bias)   # one launch
             return idx, wts
         logits = linear(h, self.w_router, self.rt, out_dtype=torch.float32)
-        K.moe_route(logits, self.groups, self.keep, self.top, idx, wts, renorm=self.renorm)
+        K.moe_route(logits, self.groups, self.keep, self.top, idx, wts, renorm=self.renorm, bias=self.router_bias)
         return idx, wts
+
+    def forward_shared(self, h: torch.Tensor):
+        """The always-on expert: ``(ys [n, hidden], gate logits [n, 1] or None)``, or None if there is none.  The caller
+        multiplies ``ys`` by ``sigmoid(gate logit)`` and adds it to the routed experts' sum."""
+        if not self.shared_inter:
+            return None
+        z = linear(h, self.w_shared_up, self.rt)
+        act = torch.empty((h.shape[0], self.shared_inter), dtype=h.dtype, device=h.device)
+        K.relu2(z[:, :self.shared_inter], act)
+        ys = linear(act, self.w_shared_down, self.rt)
+        return ys, (z[:, self.shared_inter:self.shared_inter + 1] if self.shared_gate else None)
 
     def forward_parts(self, h: torch.Tensor, ctx: StepContext) -> Tuple[torch.Tensor, torch.Tensor, int]:
         """``(y [n*top, hidden], wts [n, top], top)``: row ``n*top + k`` is the output of token ``n``'s k-th expert, not yet
@@ -101,10 +154,10 @@ class MoE:
         idx, wts = self.route(h)
         y = torch.empty((n * self.top, self.hidden), dtype=h.dtype, device=h.device)
         if self.use_grouped and n >= self.GROUPED_MIN_TOKENS:
-            K.moe_grouped(h, self.w_gate_up, self.w_down, idx, y)
+            K.moe_grouped(h, self.w_gate_up, self.w_down, idx, y, gated=self.gated)
         else:
             act = torch.empty((n * self.top, self.inter), dtype=h.dtype, device=h.device)
-            K.moe_rows(h, self.w_gate_up, idx, act, "gate_up")
+            K.moe_rows(h, self.w_gate_up, idx, act, "gate_up" if self.gated else "up_relu2")
             K.moe_rows(act, self.w_down, idx, y, "down")
         return y, wts, self.top
 
@@ -112,4 +165,6 @@ class MoE:
         y, wts, top = self.forward_parts(h, ctx)
         out = torch.empty((h.shape[0], self.hidden), dtype=h.dtype, device=h.device)
         K.moe_combine(y, wts, out)
+        if self.shared_inter:
+            raise ValueError("moe: the always-on expert is joined by the layer's arrangement (forward_parts and forward_shared)")
         return out

@@ -53,7 +53,8 @@ class OffsetRMSNorm:
     """``x / sqrt(mean(x^2) + eps) * (offset + w)``, all of it in 32-bit and rounded once: the norm whose stored weight is a
     deviation from one (``offset = 1``).  Its input may be a 32-bit stream while the output has the activation type.
     It does not offer ``rms_params`` (its arithmetic is not the one the decode products fold into themselves).
-    ``add_into`` is the form a layer with the norm on the sublayer's *output* uses: ``x32 += norm(y)``.
+    ``add_into`` is the form a layer with the norm on the sublayer's *output* uses: ``x32 += norm(y)``; ``sum_norm`` the
+    form of a layer whose norm follows the sum: ``x32 <- norm(keep * x32 + gate * y)``.
     ``params["name"]`` is the weight's tensor name behind the prefix (default ``weight``)."""
 
     @staticmethod
@@ -67,6 +68,7 @@ class OffsetRMSNorm:
         self.offset = float(params.get("offset", 1.0))
         self.rt = rt
         self.weight = weights.load(prefix + params.get("name", "weight"), "vector")  # float32 [size]
+        self._factor: Optional[torch.Tensor] = None   # offset + weight, formed when ``sum_norm`` first asks
 
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> torch.Tensor:
         n = n_rows if n_rows is not None else (rows.numel() if rows is not None else x.shape[0])
@@ -90,3 +92,18 @@ class OffsetRMSNorm:
             h = torch.empty(x32.shape, dtype=y.dtype, device=x32.device)
         K.stream_norm_add(y, self.weight, self.offset, self.eps, x32, h, wts=wts, top=top)
         return (x32 if y.dtype == torch.float32 else h) if want_h else None
+
+    def sum_norm(self, x32: torch.Tensor, y: torch.Tensor, keep: float, *, gate: Optional[torch.Tensor] = None,
+                 gate_bias: Optional[torch.Tensor] = None, wts: Optional[torch.Tensor] = None, top: int = 0,
+                 shared: Optional[torch.Tensor] = None, shared_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The norm AFTER the sum: ``x32 <- norm(keep * x32 + g * y)`` in place, ``g = sigmoid(gate + gate_bias)`` element by
+        element (1 without gate logits), sum and norm in 32-bit.  With ``wts [n, top]``, ``y`` holds ``top`` rows per row of
+        the stream (their weighted sum is formed first); ``shared`` / ``shared_gate``: one more row per token, weighted by
+        the sigmoid of its own logit.  Returns the new stream rounded to the activation type (the stream itself in the
+        32-bit path)."""
+        h = None if y.dtype == torch.float32 else torch.empty(x32.shape, dtype=y.dtype, device=x32.device)
+        if self._factor is None:
+            self._factor = self.weight if self.offset == 0.0 else (self.weight + self.offset)
+        K.gated_postnorm(y, x32, self._factor, keep, self.eps, h, gate=gate, gate_b=gate_bias, wts=wts, top=top, shared=shared,
+                         shared_gate=shared_gate)
+        return x32 if h is None else h

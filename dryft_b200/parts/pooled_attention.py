@@ -1,0 +1,150 @@
+"""Grouped-query attention over a sliding window plus one pooled key and value per block of positions that has left
+the window, with a sink in the softmax's denominator.
+
+Per step, with ``h`` the mixer's input:
+
+    q = W_q h (+ b_q), k = W_k h (+ b_k), v = W_v h (+ b_v)           one product (queries only for a run step that reads
+                                                                      another step's keys and values)
+    q, k: the first ``rotary_dim`` dims of each head rotated by the token's position (position part ``rope``), THEN
+          (``unit_norm``) each head divided by its root mean square over ``qk_dim`` (no weight, ``eps`` inside the root)
+    k, v -> the cache at the token's position; every token that completes a block of ``pool`` positions leaves the mean
+          of the block's cached keys and the mean of its cached values in pooled rows (one row per block)
+    the query at position i sees the tokens j with 0 <= i - j < window and the pooled rows of the blocks b with
+          b * pool + pool - 1 <= i - window; scores ``(q . k) * scale``; tokens and blocks share one softmax whose
+          denominator also holds ``exp(sink_head)`` (``sink``: a number per head without key or value)
+    out = W_o (heads concatenated)
+
+Without a ``window`` every earlier token is seen and there are no pooled rows.  A run step that borrows another's cache uses
+its own queries, window, pool, scale and sink over the owner's rows; when it summarises the same blocks as the owner it
+reads the owner's pooled rows, else it keeps pooled rows of its own (``CacheEntry.fills_pooled``).
+Scores, softmax, sums, angles and the unit norm are 32-bit in both precisions (``csrc/pool_attn.cu``).
+``params["names"]`` maps the tensors' roles to their names behind the prefix.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from ..cache.store import CacheEntry, KVNeed, StateNeed
+from ..config.spec import PartSpec
+from ..ops import kernels as K
+from .base import POSITIONS, Runtime, StepContext, TensorInfo, register_mixer
+from .linear import linear
+
+_ROLES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight", "q_bias": "q_proj.bias",
+          "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "sink": "sink"}
+NO_WINDOW = 1 << 30   # "every earlier token" as a window size
+
+
+def _names(params: Mapping, prefix: str) -> Dict[str, str]:
+    given = params.get("names") or {}
+    return {role: prefix + given.get(role, default) for role, default in _ROLES.items()}
+
+
+@register_mixer("pooled_window_attention")
+class PooledWindowAttention:
+    @staticmethod
+    def tensors(params: Mapping, prefix: str) -> Dict[str, TensorInfo]:
+        w, nh, nkv = params["hidden_size"], params["num_heads"], params["num_kv_heads"]
+        d, dv = params["qk_dim"], params["v_dim"]
+        nm = _names(params, prefix)
+        own, bias = params.get("own_kv", True), params.get("bias", False)
+        t = {nm["q"]: TensorInfo((nh * d, w), "matrix"), nm["o"]: TensorInfo((w, nh * dv), "matrix")}
+        if own:
+            t[nm["k"]] = TensorInfo((nkv * d, w), "matrix")
+            t[nm["v"]] = TensorInfo((nkv * dv, w), "matrix")
+        if bias:
+            t[nm["q_bias"]] = TensorInfo((nh * d,), "vector", False, 0.0)
+            if own:
+                t[nm["k_bias"]] = TensorInfo((nkv * d,), "vector", False, 0.0)
+                t[nm["v_bias"]] = TensorInfo((nkv * dv,), "vector", False, 0.0)
+        if params.get("sink", False):
+            t[nm["sink"]] = TensorInfo((nh,), "vector", False, 0.0)
+        return t
+
+    def __init__(self, params: Mapping, prefix: str, weights, rt: Runtime):
+        self.rt = rt
+        self.hidden = int(params["hidden_size"])
+        self.n_heads, self.n_kv = int(params["num_heads"]), int(params["num_kv_heads"])
+        self.qk_dim, self.v_dim = int(params["qk_dim"]), int(params["v_dim"])
+        self.scale = float(params["scale"])
+        self.eps = float(params.get("eps", 0.0))
+        self.unit_norm = bool(params.get("unit_norm", False))
+        win, pool = params.get("window"), params.get("pool")
+        self.size = int(win) if win is not None else NO_WINDOW
+        self.pool = int(pool) if (pool is not None and win is not None) else 0
+        if self.n_heads % self.n_kv or self.size < 1 or self.pool < 0:
+            raise ValueError(f"pooled_window_attention: {self.n_heads} heads over {self.n_kv} kv heads, window {win}, pool {pool}")
+        self.group = self.n_heads // self.n_kv
+        self.own_kv = bool(params.get("own_kv", True))
+        self.q_dim, self.o_dim = self.n_heads * self.qk_dim, self.n_heads * self.v_dim
+        nm = _names(params, prefix)
+        if self.own_kv:
+            self.w_in = weights.load_fused([nm["q"], nm["k"], nm["v"]],
+                                           [self.q_dim, self.n_kv * self.qk_dim, self.n_kv * self.v_dim], self.hidden)
+        else:
+            self.w_in = weights.load(nm["q"], "matrix")
+        self.w_o = weights.load(nm["o"], "matrix")
+        bias = bool(params.get("bias", False))
+        self.q_bias = weights.load(nm["q_bias"], "vector") if bias else None
+        self.k_bias = weights.load(nm["k_bias"], "vector") if bias and self.own_kv else None
+        self.v_bias = weights.load(nm["v_bias"], "vector") if bias and self.own_kv else None
+        self.sink = weights.load(nm["sink"], "vector") if params.get("sink", False) else None
+        pos: PartSpec = params.get("position") or PartSpec("none")
+        self.position = POSITIONS.get(pos.kind)(pos.params, self.qk_dim, rt)
+        if getattr(self.position, "interleaved", False):
+            raise ValueError("pooled_window_attention: its kernels rotate dims j and j + R/2 together")
+        self.rot = int(getattr(self.position, "rotary_dim", 0) or 0) if getattr(self.position, "inv_freq", None) is not None else 0
+        K.pool_attention_lib(self.qk_dim, self.v_dim, self.group)   # build (or find) the kernels of this head shape now
+        self.use_prefill_kernel = rt.is_bf16 and K.pool_attention_prefill_supported(self.qk_dim, self.v_dim, self.group)
+
+    def kv_need(self) -> Optional[KVNeed]:
+        if self.size >= NO_WINDOW:
+            return KVNeed(self.n_kv, self.qk_dim, None, self.v_dim)
+        # rows that must stay: the window's, and those of the block that is still to be summarised
+        return KVNeed(self.n_kv, self.qk_dim, max(self.size, self.pool), self.v_dim, None, True, self.pool or None)
+
+    def state_need(self) -> Optional[StateNeed]:
+        return None
+
+    def _n_splits(self, n_rows: int, max_kv: int) -> int:
+        """Keys of a row split over enough blocks to fill the device, a block taking at least 128 keys."""
+        keys = min(max(1, max_kv), self.size) + (max(1, max_kv) // self.pool if self.pool else 0)
+        want = math.ceil(2 * self.rt.sm_count / max(1, n_rows * self.n_kv))
+        return max(1, min(32, want, (keys + 127) // 128))
+
+    def forward(self, h: torch.Tensor, ctx: StepContext, cache: CacheEntry, state, owns_cache: bool = True) -> torch.Tensor:
+        if owns_cache != self.own_kv:
+            raise ValueError("pooled_window_attention: a layer without key and value projections must read another run step's cache")
+        n, dev = h.shape[0], h.device
+        proj = linear(h, self.w_in, self.rt)
+        q = torch.empty((n, self.n_heads, self.qk_dim), dtype=h.dtype, device=dev)
+        pos = self.position
+        K.pool_attn_prep(proj, self.q_bias, self.k_bias, self.v_bias, pos.inv_freq if self.rot else None,
+                         getattr(pos, "inv_freq_lo", None) if self.rot else None, self.rot, ctx.tok_slot, ctx.tok_pos, q, cache.k,
+                         cache.v, cache.page_table, self.n_heads, self.n_kv, self.eps if self.unit_norm else -1.0, owns_cache)
+        pooled = None
+        if self.pool:
+            pc = cache.pooled
+            if pc is None:
+                raise ValueError("pooled_window_attention: the cache holds no pooled rows for this run step")
+            pooled = (pc.k, pc.v, pc.page_table)
+            if cache.fills_pooled:
+                K.pool_attn_blocks(cache.k, cache.v, cache.page_table, pc.k, pc.v, pc.page_table, ctx.tok_slot, ctx.tok_pos, n,
+                                   self.pool, self.group)
+        o = torch.empty((n, self.n_heads, self.v_dim), dtype=h.dtype, device=dev)
+        if self.use_prefill_kernel and not ctx.decode and ctx.n_tiles > 0:
+            K.pool_attn_prefill(q, cache.k, cache.v, cache.page_table, pooled, self.sink, ctx.tile_tok0, ctx.tile_rows, ctx.tok_slot,
+                                ctx.tok_pos, o, ctx.n_tiles, self.scale, self.size, self.pool)
+        else:
+            s = self._n_splits(n, ctx.max_kv)
+            part_o = part_ml = None
+            if s > 1:
+                part_o = torch.empty((n, self.n_heads, s, self.v_dim), dtype=torch.float32, device=dev)
+                part_ml = torch.empty((n, self.n_heads, s, 2), dtype=torch.float32, device=dev)
+            K.pool_attn_rows(q, cache.k, cache.v, cache.page_table, pooled, self.sink, ctx.tok_slot, ctx.tok_pos, o, self.scale,
+                             self.size, self.pool, s, part_o, part_ml)
+        return linear(o.view(n, self.o_dim), self.w_o, self.rt)

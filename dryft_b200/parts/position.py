@@ -25,12 +25,28 @@ from .base import Runtime, StepContext, register_position
 TABLE_MIN_TOKENS = 64   # below this every warp evaluates its own angles
 
 
+def scale_by_wavelength(freq: torch.Tensor, scaling: Mapping) -> torch.Tensor:
+    """Rotary frequencies (float64) with long waves slowed: see ``Rope``."""
+    import math
+
+    factor, low, high, orig = (float(scaling[k]) for k in ("factor", "low", "high", "original"))
+    if not (factor > 0 and high > low and orig > 0):
+        raise ValueError(f"rope scaling: factor and original must be positive and high above low, got {dict(scaling)}")
+    wave = 2.0 * math.pi / freq
+    s = ((orig / wave - low) / (high - low)).clamp(0.0, 1.0)
+    blended = (1.0 - s) * freq / factor + s * freq
+    return torch.where(wave < orig / high, freq, torch.where(wave > orig / low, freq / factor, blended))
+
+
 @register_position("rope")
 class Rope:
     """``params["layout"]``: ``"half"`` (dims ``j`` and ``j + R/2`` turn together; the default) or ``"interleaved"`` (dims
     ``2j`` and ``2j + 1``); the mixers whose kernels take both read ``interleaved``.  ``params["freq"]``: ``"float32"``
     (the reference's expression, evaluated in 32-bit; the default) or ``"rounded_once"`` (``theta^(-2j/R)`` evaluated in
-    64-bit and rounded to 32-bit once; what that rounding drops is kept as ``inv_freq_lo`` for kernels that take the pair)."""
+    64-bit and rounded to 32-bit once; what that rounding drops is kept as ``inv_freq_lo`` for kernels that take the pair).
+    ``params["scaling"]`` (needs ``freq="rounded_once"``): a mapping ``factor, low, high, original`` that slows long waves: with
+    the wavelength ``l = 2 pi / f``, ``f`` stays where ``l < original / high``, becomes ``f / factor`` where ``l > original /
+    low``, and in between ``(1 - s) f / factor + s f`` with ``s = (original / l - low) / (high - low)``."""
 
     def __init__(self, params: Mapping, head_dim: int, rt: Runtime):
         self.rotary_dim = int(params.get("rotary_dim", head_dim))
@@ -45,9 +61,13 @@ class Rope:
         self.inv_freq_lo: Optional[torch.Tensor] = None
         if params.get("freq", "float32") == "rounded_once":
             exact = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -torch.arange(0, r, 2, dtype=torch.float64) / r)
+            if params.get("scaling") is not None:
+                exact = scale_by_wavelength(exact, params["scaling"])
             inv_freq = exact.to(torch.float32)
             self.inv_freq_lo = (exact - inv_freq.to(torch.float64)).to(torch.float32).to(rt.device)
         else:
+            if params.get("scaling") is not None:
+                raise ValueError("rope: frequency scaling is evaluated in 64-bit; ask for freq='rounded_once' with it")
             inv_freq = 1.0 / (self.theta ** (torch.arange(0, r, 2, dtype=torch.int64).to(torch.float32) / r))
         self.inv_freq: Optional[torch.Tensor] = inv_freq.to(rt.device)
         self.dtype = rt.dtype
