@@ -128,6 +128,45 @@ PRESETS.update({
 EQUAL_SIZE.update({"vobusun-1k": "qwen3-1k", "vobusun-2k": "qwen3-2k"})
 
 
+def _mogelix(width: int, layers: int, heads: int, kv_heads: int, dim: int, window: int, pool: int, experts: int, ff: int, top: int,
+             vocab: int, ssm_heads: int, ssm_vdim: int, state: int, share_every: int = 3, ssm_every: int = 4) -> dict:
+    """A Mogelix ``config.json``: every ``ssm_every``-th layer is a state-space mixer; of the attention layers every
+    ``share_every``-th reads the keys and values of the nearest earlier attention layer that has its own.  The first layer's
+    feed-forward is dense (the size of the experts a token uses plus the always-on one), the others are routed."""
+    rot = {"dims": dim, "base": 1000000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    out, owner, n_att = [], None, 0
+    for i in range(layers):
+        mlp = {"kind": "dense", "ff": ff * (top + 1)} if i == 0 else \
+            {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}, "shared": {"ff": ff}}
+        if ssm_every and i % ssm_every == ssm_every - 1:
+            out.append({"type": "mamba2", "mlp": mlp,
+                        "mixer": {"heads": ssm_heads, "vdim": ssm_vdim, "state": state, "groups": 1, "conv": 4, "norm_groups": 1}})
+            continue
+        mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                 "mask": {"size": window, "pool": pool}, "rot": rot}
+        n_att += 1
+        if share_every and owner is not None and n_att % share_every == 0:
+            mixer["kv_from"] = owner
+        else:
+            owner = i
+        out.append({"type": "attention", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Mogelix", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "postln_alpha": 2.0, "layers": out}
+
+
+# Mogelix shapes with layers the size of a real model's, and beside each the closest design at equal size: the Tevovik shape
+# of the same width, layer count, head counts, expert count and size, experts a token uses and vocabulary (queries and keys
+# of 128 against maps of 64 twice; the window equals the chunk).
+PRESETS.update({
+    "mogelix-tiny": _mogelix(width=64, layers=5, heads=4, kv_heads=2, dim=16, window=40, pool=8, experts=6, ff=32, top=2, vocab=256,
+                             ssm_heads=4, ssm_vdim=16, state=16),
+    "mogelix-1k": _mogelix(width=1024, layers=8, heads=8, kv_heads=2, dim=128, window=1024, pool=64, experts=32, ff=512, top=4,
+                           vocab=32768, ssm_heads=16, ssm_vdim=128, state=128),
+    "mogelix-2k": _mogelix(width=2048, layers=12, heads=16, kv_heads=4, dim=128, window=2048, pool=64, experts=64, ff=768, top=8,
+                           vocab=65536, ssm_heads=32, ssm_vdim=128, state=128),
+})
+EQUAL_SIZE.update({"mogelix-1k": "tevovik-1k", "mogelix-2k": "tevovik-2k"})
+
+
 def preset(name: str) -> dict:
     if name not in PRESETS:
         raise KeyError(f"unknown preset {name!r}; known: " + ", ".join(sorted(PRESETS)))

@@ -14,6 +14,16 @@ from typing import Callable, Dict, List, Mapping, Optional
 import torch
 
 F = torch.float64
+_ROUND: Optional[torch.dtype] = None      # set by ``forward(..., rounding=...)``: products read and leave values of this type
+
+
+def rnd(x: torch.Tensor) -> torch.Tensor:
+    return x if _ROUND is None else x.to(_ROUND).to(F)
+
+
+def mm(h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``h @ w.T``; with a rounding type set, of the rounded ``h`` and rounded itself (what a 16-bit product does)."""
+    return rnd(rnd(h) @ w.T)
 
 
 def rms_unit(x: torch.Tensor, eps: float) -> torch.Tensor:
@@ -86,8 +96,8 @@ def pooled_window_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, s
     G = k.shape[1]
     rep = H // G
     nb = L // pool
-    kb = k[: nb * pool].reshape(nb, pool, G, -1).mean(1) if nb else k[:0]
-    vb = v[: nb * pool].reshape(nb, pool, G, -1).mean(1) if nb else v[:0]
+    kb = rnd(k[: nb * pool].reshape(nb, pool, G, -1).mean(1)) if nb else k[:0]
+    vb = rnd(v[: nb * pool].reshape(nb, pool, G, -1).mean(1)) if nb else v[:0]
     out = torch.zeros(L, H, v.shape[-1], dtype=F)
     for i in range(L):
         toks, blocks = visible(i, size, pool)
@@ -107,9 +117,9 @@ def attention_keys_values(h: torch.Tensor, p: Mapping, w: Mapping[str, torch.Ten
     L = h.shape[0]
     G, d, dv = int(p["kv_heads"]), int(p["dim"]), int(p["vdim"])
     pos = torch.arange(L)
-    k = (h @ w[pre + "k"].T + w[pre + "k.b"]).reshape(L, G, d)
-    v = (h @ w[pre + "v"].T + w[pre + "v.b"]).reshape(L, G, dv)
-    k = rms_unit(rotate(k, pos, rotary_frequencies(p["rot"])), eps)
+    k = (mm(h, w[pre + "k"]) + w[pre + "k.b"]).reshape(L, G, d)
+    v = rnd(mm(h, w[pre + "v"]) + w[pre + "v.b"]).reshape(L, G, dv)
+    k = rnd(rms_unit(rotate(k, pos, rotary_frequencies(p["rot"])), eps))
     return k, v
 
 
@@ -117,11 +127,11 @@ def attention_mixer(h: torch.Tensor, p: Mapping, w: Mapping[str, torch.Tensor], 
     """``kv``: the (keys, values) this layer reads -- its own or an earlier layer's."""
     L = h.shape[0]
     H, d = int(p["heads"]), int(p["dim"])
-    q = (h @ w[pre + "q"].T + w[pre + "q.b"]).reshape(L, H, d)
-    q = rms_unit(rotate(q, torch.arange(L), rotary_frequencies(p["rot"])), eps)
+    q = (mm(h, w[pre + "q"]) + w[pre + "q.b"]).reshape(L, H, d)
+    q = rnd(rms_unit(rotate(q, torch.arange(L), rotary_frequencies(p["rot"])), eps))
     k, v = kv
     o = pooled_window_attention(q, k, v, w[pre + "sink"], float(p["scale"]), int(p["mask"]["size"]), int(p["mask"]["pool"]))
-    return o.reshape(L, -1) @ w[pre + "o"].T
+    return mm(o.reshape(L, -1), w[pre + "o"])
 
 
 # ----------------------------------------------------------------------------- state-space mixer
@@ -156,7 +166,7 @@ def mamba2_mixer(h: torch.Tensor, p: Mapping, w: Mapping[str, torch.Tensor], pre
     L = h.shape[0]
     Hh, dv, N, Gg = int(p["heads"]), int(p["vdim"]), int(p["state"]), int(p["groups"])
     inner = Hh * dv
-    proj = h @ w[pre + "in"].T
+    proj = rnd(h) @ w[pre + "in"].T
     z, xbc, dt = proj[:, :inner], proj[:, inner:2 * inner + 2 * Gg * N], proj[:, 2 * inner + 2 * Gg * N:]
     xbc = silu(causal_conv(xbc, w[pre + "conv"], w[pre + "conv.b"]))
     x = xbc[:, :inner].reshape(L, Hh, dv)
@@ -167,7 +177,7 @@ def mamba2_mixer(h: torch.Tensor, p: Mapping, w: Mapping[str, torch.Tensor], pre
     y = y * silu(z)
     parts = int(p["norm_groups"])
     y = rms_unit(y.reshape(L, parts, inner // parts), eps).reshape(L, inner) * w[pre + "norm"]
-    return y @ w[pre + "o"].T
+    return mm(y, w[pre + "o"])
 
 
 # ----------------------------------------------------------------------------- feed-forward
@@ -177,16 +187,16 @@ def poly_norm(z: torch.Tensor, coef: torch.Tensor, eps: float) -> torch.Tensor:
 
 
 def dense_ffn(h: torch.Tensor, w: Mapping[str, torch.Tensor], pre: str, eps: float) -> torch.Tensor:
-    return poly_norm(h @ w[pre + "up"].T, w[pre + "act"], eps) @ w[pre + "down"].T
+    return mm(poly_norm(mm(h, w[pre + "up"]), w[pre + "act"], eps), w[pre + "down"])
 
 
 def relu2_expert(h: torch.Tensor, up: torch.Tensor, down: torch.Tensor) -> torch.Tensor:
-    return torch.relu(h @ up.T) ** 2 @ down.T
+    return mm(torch.relu(mm(h, up)) ** 2, down)
 
 
 def route(h: torch.Tensor, wr: torch.Tensor, br: torch.Tensor, top: int):
     """Chosen experts ``[L, top]`` and their weights: a softmax over the chosen logits only."""
-    z = h @ wr.T + br
+    z = rnd(h) @ wr.T + br
     val, idx = torch.topk(z, top, dim=-1)
     return idx, torch.softmax(val, -1)
 
@@ -201,14 +211,25 @@ def moe_ffn(h: torch.Tensor, p: Mapping, w: Mapping[str, torch.Tensor], pre: str
         out = out + gate * ye
     if p.get("shared") is not None:
         ys = relu2_expert(h, w[pre + "shared.up"], w[pre + "shared.down"])
-        out = out + torch.sigmoid(h @ w[pre + "shared.sg"].T) * ys
+        out = out + torch.sigmoid(mm(h, w[pre + "shared.sg"])) * ys
     return out
 
 
 # ----------------------------------------------------------------------------- the model
 def forward(config: Mapping, weights: Mapping[str, torch.Tensor], tokens: List[int],
-            tap: Optional[Callable[[int, torch.Tensor], None]] = None) -> torch.Tensor:
-    """Logits ``[L, vocab]`` (float64) of one sequence.  ``tap(i, x)`` is called with the stream after layer ``i``."""
+            tap: Optional[Callable[[int, torch.Tensor], None]] = None, rounding: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Logits ``[L, vocab]`` (float64) of one sequence.  ``tap(i, x)`` is called with the stream after layer ``i``.
+    ``rounding=torch.bfloat16`` rounds what enters and leaves every matrix product and what a cache would hold (the
+    stream, norms, scores, routers and recurrences stay exact): how far 16-bit arithmetic alone moves the logits."""
+    global _ROUND
+    _ROUND = rounding
+    try:
+        return _forward(config, weights, tokens, tap)
+    finally:
+        _ROUND = None
+
+
+def _forward(config, weights, tokens, tap):
     w = {k: v.to(F) for k, v in weights.items() if v.is_floating_point()}
     eps = float(config["norm"]["eps"])
     alpha = float(config["postln_alpha"])
@@ -227,7 +248,7 @@ def forward(config: Mapping, weights: Mapping[str, torch.Tensor], tokens: List[i
             y = mamba2_mixer(x, p, w, pre + "mix.", eps)
         else:
             raise ValueError(layer["type"])
-        y = y * torch.sigmoid(x @ w[pre + "rg1"].T + w[pre + "rg1.b"])
+        y = y * torch.sigmoid(mm(x, w[pre + "rg1"]) + w[pre + "rg1.b"])
         x = rms_norm(alpha * x + y, w[pre + "norm1"], eps)
         mlp = layer.get("mlp")
         if mlp is not None:
@@ -237,8 +258,18 @@ def forward(config: Mapping, weights: Mapping[str, torch.Tensor], tokens: List[i
                 y = moe_ffn(x, mlp, w, pre + "mlp.")
             else:
                 raise ValueError(mlp["kind"])
-            y = y * torch.sigmoid(x @ w[pre + "rg2"].T + w[pre + "rg2.b"])
+            y = y * torch.sigmoid(mm(x, w[pre + "rg2"]) + w[pre + "rg2.b"])
             x = rms_norm(alpha * x + y, w[pre + "norm2"], eps)
         if tap is not None:
             tap(i, x)
-    return rms_norm(x, w["final.norm"], eps) @ w["head"].T
+    return rnd(rms_norm(x, w["final.norm"], eps)) @ w["head"].T
+
+
+def greedy(config: Mapping, weights: Mapping[str, torch.Tensor], prompt: List[int], n_new: int) -> List[int]:
+    """The best next token, ``n_new`` times, each from a whole evaluation of all tokens so far."""
+    ids, out = list(prompt), []
+    for _ in range(n_new):
+        t = int(torch.argmax(forward(config, weights, ids)[-1]))
+        out.append(t)
+        ids.append(t)
+    return out
