@@ -16,6 +16,11 @@
 //   ssm_scan    one block per (sequence, head, slice of WARPS value columns); a warp owns one column p of S, a lane the
 //               rows n = lane, lane + 32, ...; tokens in order, the next token's operands requested before the current
 //               token's arithmetic; y_t[p] is a warp sum.
+//   chunked     a step of many tokens is cut into chunks of `cht` tokens that run side by side, in three launches: (1) every
+//               chunk walks its tokens from a ZERO state and leaves that state and the product of its decays; (2) a prefix
+//               over each sequence's chunks, S_start(c+1) = decay(c) S_start(c) + S_own(c), turns these into the state every
+//               chunk starts from and leaves the sequence's final state in the slot; (3) every chunk walks its tokens again
+//               from its start state and writes y.  Twice the arithmetic, 1 / chunks of the dependent steps.
 // Sequences with slot -1 (padding) are skipped.  No block waits on another block.
 #include "common.cuh"
 #include <math.h>
@@ -76,27 +81,48 @@ __global__ void __launch_bounds__(CONV_THREADS) ssm_tail_kernel(
 
 __device__ __forceinline__ float softplusf_(float v) { return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v))); }
 
+// chunk `ci` of the step (chunks counted through the sequences in order) -> its sequence and its index within it
+__device__ __forceinline__ bool chunk_of(const int* __restrict__ cu_q, int n_seqs, int cht, int ci, int* b_out, int* c_out) {
+  int base = 0;
+  for (int b = 0; b < n_seqs; ++b) {
+    const int nc = (cu_q[b + 1] - cu_q[b] + cht - 1) / cht;
+    if (ci < base + nc) { *b_out = b; *c_out = ci - base; return true; }
+    base += nc;
+  }
+  return false;
+}
+
+// MODE 0: block x = sequence; its tokens in order from the slot's state, which is left advanced.
+// MODE 1: block x = chunk; from a zero state; leaves the chunk's own state in cstate[chunk] and its decays' product in cdec.
+// MODE 2: block x = chunk; from the start state in cstate[chunk]; writes y.
+template <int MODE>
 __global__ void __launch_bounds__(SCAN_WARPS * 32) ssm_scan_kernel(
     const float* __restrict__ xbc, int CH, const float* __restrict__ proj, int ld, int dt_off, const float* __restrict__ dt_bias,
     const float* __restrict__ a_log, const float* __restrict__ Dp, const int* __restrict__ cu_q, const int* __restrict__ seq_slot,
-    int heads, int groups, int N, int dv, float* __restrict__ state, float* __restrict__ y) {
-  const int b = blockIdx.x, hd = blockIdx.y;
+    int n_seqs, int cht, int heads, int groups, int N, int dv, float* __restrict__ state, float* __restrict__ cstate,
+    float* __restrict__ cdec, float* __restrict__ y) {
+  const int hd = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int p = blockIdx.z * SCAN_WARPS + warp;
+  int b = blockIdx.x, c = 0;
+  if (MODE != 0 && !chunk_of(cu_q, n_seqs, cht, blockIdx.x, &b, &c)) return;
   const int slot = seq_slot[b];
   if (slot < 0 || p >= dv) return;
-  const int t0 = cu_q[b], t1 = cu_q[b + 1];
+  int t0 = cu_q[b], t1 = cu_q[b + 1];
+  if (MODE != 0) { t0 += c * cht; t1 = min(t1, t0 + cht); }
   if (t1 <= t0) return;
   const int inner = heads * dv, g = hd / (heads / groups);
   const int xo = hd * dv + p, bo = inner + g * N, co = inner + groups * N + g * N;
   const float rate = expf(a_log[hd]), bias = dt_bias[hd], dskip = Dp[hd];
-  float* sp = state + (((size_t)slot * heads + hd) * N) * dv + p;
+  float* sp = MODE == 0 ? state + (((size_t)slot * heads + hd) * N) * dv + p
+                        : cstate + (((size_t)blockIdx.x * heads + hd) * N) * dv + p;
   float S[MAX_NR];
 #pragma unroll
   for (int r = 0; r < MAX_NR; ++r) {
     const int n = lane + 32 * r;
-    S[r] = n < N ? sp[(size_t)n * dv] : 0.f;
+    S[r] = (MODE != 1 && n < N) ? sp[(size_t)n * dv] : 0.f;
   }
+  float dprod = 1.f;
   float Bn[MAX_NR], Cn[MAX_NR], xv, dtr;
   auto fetch = [&](int t) {
     const float* row = xbc + (size_t)t * CH;
@@ -117,20 +143,52 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) ssm_scan_kernel(
     const float x = xv, dt = softplusf_(dtr + bias);
     if (t + 1 < t1) fetch(t + 1);
     const float decay = expf(-rate * dt), dx = dt * x;
-    float acc = 0.f;
+    if (MODE == 1) {
+      dprod *= decay;
+#pragma unroll
+      for (int r = 0; r < MAX_NR; ++r) S[r] = fmaf(decay, S[r], Bc[r] * dx);
+    } else {
+      float acc = 0.f;
+#pragma unroll
+      for (int r = 0; r < MAX_NR; ++r) {
+        S[r] = fmaf(decay, S[r], Bc[r] * dx);
+        acc = fmaf(S[r], Cc[r], acc);
+      }
+      acc = warp_sum(acc);
+      if (lane == 0) y[(size_t)t * inner + xo] = fmaf(dskip, x, acc);
+    }
+  }
+  if (MODE != 2) {
 #pragma unroll
     for (int r = 0; r < MAX_NR; ++r) {
-      S[r] = fmaf(decay, S[r], Bc[r] * dx);
-      acc = fmaf(S[r], Cc[r], acc);
+      const int n = lane + 32 * r;
+      if (n < N) sp[(size_t)n * dv] = S[r];
     }
-    acc = warp_sum(acc);
-    if (lane == 0) y[(size_t)t * inner + xo] = fmaf(dskip, x, acc);
   }
-#pragma unroll
-  for (int r = 0; r < MAX_NR; ++r) {
-    const int n = lane + 32 * r;
-    if (n < N) sp[(size_t)n * dv] = S[r];
+  if (MODE == 1 && p == 0 && lane == 0) cdec[(size_t)blockIdx.x * heads + hd] = dprod;
+}
+
+// S_start(c + 1) = decay(c) S_start(c) + S_own(c) over a sequence's chunks, from the slot's state; cstate[c] turns from the
+// chunk's own state into its start state, and the slot's state becomes the state after the last chunk.
+__global__ void __launch_bounds__(256) ssm_chunk_prefix_kernel(const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int cht,
+                                                               int heads, int per_head, float* __restrict__ state,
+                                                               float* __restrict__ cstate, const float* __restrict__ cdec) {
+  const int b = blockIdx.x, hd = blockIdx.y;
+  const int e = blockIdx.z * 256 + threadIdx.x;
+  const int slot = seq_slot[b];
+  if (slot < 0 || e >= per_head) return;
+  int base = 0;
+  for (int i = 0; i < b; ++i) base += (cu_q[i + 1] - cu_q[i] + cht - 1) / cht;
+  const int nc = (cu_q[b + 1] - cu_q[b] + cht - 1) / cht;
+  float* sp = state + ((size_t)slot * heads + hd) * per_head + e;
+  float carry = *sp;
+  for (int c = 0; c < nc; ++c) {
+    float* cs = cstate + ((size_t)(base + c) * heads + hd) * per_head + e;
+    const float own = *cs;
+    *cs = carry;
+    carry = fmaf(cdec[(size_t)(base + c) * heads + hd], carry, own);
   }
+  *sp = carry;
 }
 }  // namespace
 
@@ -152,7 +210,32 @@ DRYFT_API int dryft_ssm_scan(const float* xbc, int CH, const float* proj, int ld
   if (heads < 1 || groups < 1 || heads % groups || N < 1 || N > 32 * MAX_NR || dv < 1 || heads > 65535) return DRYFT_ERR_UNSUPPORTED;
   dim3 grid(n_seqs, heads, (dv + SCAN_WARPS - 1) / SCAN_WARPS);
   if (grid.z > 65535) return DRYFT_ERR_UNSUPPORTED;
-  ssm_scan_kernel<<<grid, SCAN_WARPS * 32, 0, st>>>(xbc, CH, proj, ld, dt_off, dt_bias, a_log, Dp, cu_q, seq_slot, heads, groups, N, dv,
-                                                   state, y);
+  ssm_scan_kernel<0><<<grid, SCAN_WARPS * 32, 0, st>>>(xbc, CH, proj, ld, dt_off, dt_bias, a_log, Dp, cu_q, seq_slot, n_seqs, 0, heads,
+                                                      groups, N, dv, state, nullptr, nullptr, y);
+  return launch_status();
+}
+
+// The same recurrence with the step cut into chunks of `cht` tokens (three launches).  `n_chunks` bounds the step's chunks
+// (tokens / cht + sequences); cstate [n_chunks, heads, N, dv] and cdec [n_chunks, heads] are scratch.
+DRYFT_API int dryft_ssm_scan_chunked(const float* xbc, int CH, const float* proj, int ld, int dt_off, const float* dt_bias,
+                                     const float* a_log, const float* Dp, const int* cu_q, const int* seq_slot, int n_seqs, int cht,
+                                     int n_chunks, int heads, int groups, int N, int dv, float* state, float* cstate, float* cdec,
+                                     float* y, cudaStream_t st) {
+  if (n_seqs <= 0 || n_chunks <= 0) return 0;
+  if (heads < 1 || groups < 1 || heads % groups || N < 1 || N > 32 * MAX_NR || dv < 1 || heads > 65535 || cht < 1 || n_seqs > 65535)
+    return DRYFT_ERR_UNSUPPORTED;
+  dim3 grid(n_chunks, heads, (dv + SCAN_WARPS - 1) / SCAN_WARPS);
+  const int per_head = N * dv;
+  dim3 grid_b(n_seqs, heads, (per_head + 255) / 256);
+  if (grid.z > 65535 || grid_b.z > 65535) return DRYFT_ERR_UNSUPPORTED;
+  ssm_scan_kernel<1><<<grid, SCAN_WARPS * 32, 0, st>>>(xbc, CH, proj, ld, dt_off, dt_bias, a_log, Dp, cu_q, seq_slot, n_seqs, cht, heads,
+                                                      groups, N, dv, state, cstate, cdec, y);
+  int rc = launch_status();
+  if (rc) return rc;
+  ssm_chunk_prefix_kernel<<<grid_b, 256, 0, st>>>(cu_q, seq_slot, cht, heads, per_head, state, cstate, cdec);
+  rc = launch_status();
+  if (rc) return rc;
+  ssm_scan_kernel<2><<<grid, SCAN_WARPS * 32, 0, st>>>(xbc, CH, proj, ld, dt_off, dt_bias, a_log, Dp, cu_q, seq_slot, n_seqs, cht, heads,
+                                                      groups, N, dv, state, cstate, cdec, y);
   return launch_status();
 }

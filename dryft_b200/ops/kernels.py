@@ -1661,7 +1661,11 @@ def ssm_lib() -> ctypes.CDLL:
     return _single_lib("ssm", {
         "dryft_ssm_conv": [_p, _i, _i, _i, _p, _p, _i, _p, _p, _i, _p, _p, _i, _p],
         "dryft_ssm_scan": [_p, _i, _p, _i, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p, _p],
+        "dryft_ssm_scan_chunked": [_p, _i, _p, _i, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p],
     })
+
+
+SSM_CHUNK_TOKENS = 128    # tokens a chunk of a many-token step walks in order (more for steps of more than 8,192 tokens)
 
 
 def ssm_conv(proj, x_off: int, conv_w, conv_b, cu_q, seq_slot, n_seqs: int, tail, out) -> None:
@@ -1686,7 +1690,7 @@ def ssm_conv(proj, x_off: int, conv_w, conv_b, cu_q, seq_slot, n_seqs: int, tail
 
 
 def ssm_scan(xbc, proj, dt_off: int, dt_bias, a_log, d_skip, cu_q, seq_slot, n_seqs: int, heads: int, groups: int, n_state: int,
-             vdim: int, state, y) -> None:
+             vdim: int, state, y, chunked: bool = False) -> None:
     """The recurrence ``S_t = exp(-exp(a_log) dt_t) S_(t-1) + dt_t B_t x_t^T``, ``y_t = S_t^T C_t + D x_t`` per head, with
     ``dt_t = softplus(proj[t, dt_off + head] + dt_bias)``; ``xbc [n, heads*vdim + 2*groups*n_state]`` holds x, B, C after
     the convolution; ``state [slots, heads, n_state, vdim]`` float32 is read and left advanced; ``y [n, heads*vdim]``."""
@@ -1702,6 +1706,17 @@ def ssm_scan(xbc, proj, dt_off: int, dt_bias, a_log, d_skip, cu_q, seq_slot, n_s
         _need(t, nm, torch.int32)
     if dt_off < 0 or dt_off + heads > proj.shape[1]:
         raise KernelError(f"ssm_scan: {heads} step sizes from column {dt_off} of a row of {proj.shape[1]}")
+    if chunked:
+        # a step of many tokens: chunks side by side (own states from zero, a prefix over them, outputs from the start states)
+        cht = max(SSM_CHUNK_TOKENS, -(-n // 64 // 32) * 32)
+        n_chunks = n // cht + int(n_seqs)
+        cstate = torch.empty((n_chunks, heads, n_state, vdim), dtype=torch.float32, device=xbc.device)
+        cdec = torch.empty((n_chunks, heads), dtype=torch.float32, device=xbc.device)
+        _ok(ssm_lib().dryft_ssm_scan_chunked(_ptr(xbc), ch, _ptr(proj), proj.shape[1], int(dt_off), _ptr(dt_bias), _ptr(a_log),
+                                             _ptr(d_skip), _ptr(cu_q), _ptr(seq_slot), int(n_seqs), cht, n_chunks, heads, groups,
+                                             n_state, vdim, _ptr(state), _ptr(cstate), _ptr(cdec), _ptr(y), _stream()),
+            f"ssm_scan_chunked ({heads} heads, state {n_state} x {vdim})", n_kernels=3)
+        return
     _ok(ssm_lib().dryft_ssm_scan(_ptr(xbc), ch, _ptr(proj), proj.shape[1], int(dt_off), _ptr(dt_bias), _ptr(a_log), _ptr(d_skip),
                                  _ptr(cu_q), _ptr(seq_slot), int(n_seqs), heads, groups, n_state, vdim, _ptr(state), _ptr(y),
                                  _stream()), f"ssm_scan ({heads} heads, state {n_state} x {vdim})")
@@ -1733,9 +1748,60 @@ def pool_attention_lib(qk_dim: int, v_dim: int, group: int) -> ctypes.CDLL:
         return lib
 
 
-def pool_attention_prefill_supported(qk_dim: int, v_dim: int, group: int) -> bool:
-    """Whether the tensor-core prompt kernel of the pooled-window attention takes this head shape."""
-    return False
+def pool_attention_prefill_supported(qk_dim: int, v_dim: int, group: int, page: int = 64) -> bool:
+    """Whether the tensor-core prompt kernel of the pooled-window attention takes this head shape (k16 steps over the keys,
+    n8 pairs over the values, 64-token pages, two stages of a key and a value tile in shared memory)."""
+    return (qk_dim > 0 and qk_dim % 16 == 0 and qk_dim <= 256 and v_dim > 0 and v_dim % 16 == 0 and v_dim <= 256
+            and page == 64 and 1 <= group <= 16 and 2 * ((64 + 128) * (qk_dim + 8) + 128 * (v_dim + 8)) <= 227 * 1024)
+
+
+def pool_attention_prefill_lib(qk_dim: int, v_dim: int, group: int, page: int = 64) -> ctypes.CDLL:
+    if not pool_attention_prefill_supported(qk_dim, v_dim, group, page):
+        raise KernelError(f"pooled-window prompt attention takes key and value sizes in steps of 16 and 64-token pages, got "
+                          f"{qk_dim}, {v_dim}, {page}")
+    key = ("pool_prefill", qk_dim, v_dim, group, page)
+    with _lock:
+        lib = _variants.get(key)
+        if lib is None:
+            path = build.build_library("pool_attn_prefill", ("pool_attn_prefill.cu",),
+                                       {"DRYFT_QK_DIM": qk_dim, "DRYFT_V_DIM": v_dim, "DRYFT_GROUP": group, "DRYFT_PAGE": page})
+            lib = _load(path)
+            lib.dryft_pool_attn_prefill.argtypes = [_p, _p, _p, _p, _i, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _f,
+                                                    _i, _i, _p]
+            lib.dryft_pool_attn_prefill.restype = _i
+            if (lib.dryft_pool_attn_prefill_qk_dim(), lib.dryft_pool_attn_prefill_v_dim()) != (qk_dim, v_dim):
+                raise KernelError("pooled-window prompt attention: the library was built for another head shape")
+            _variants[key] = lib
+        return lib
+
+
+def pool_attn_prefill(q, k_pages, v_pages, page_table, pooled, sink, tile_tok0, tile_rows, tok_slot, tok_pos, out, n_tiles: int,
+                      scale: float, size: int, pool: int) -> None:
+    """Prompt attention (bfloat16) of ``q [n, H, D]``, tile by tile of up to 64 tokens of one sequence, over the last ``size``
+    cached tokens and the pooled rows of the blocks of ``pool`` positions wholly before them (``pooled = (pk_pages, pv_pages,
+    pool_table)``; ``pool = 0``: none); the softmax's denominator also holds ``exp(sink[head])`` (if given)."""
+    n, n_heads, d = q.shape
+    n_kv, page = k_pages.shape[1], k_pages.shape[2]
+    dv = v_pages.shape[-1]
+    _need(q, "q", torch.bfloat16)
+    _need(k_pages, "k_pages", q.dtype, (None, n_kv, page, d))
+    _need(v_pages, "v_pages", q.dtype, (None, n_kv, page, dv))
+    _need(out, "out", q.dtype, (n, n_heads, dv))
+    _need(page_table, "page_table", torch.int32)
+    if sink is not None:
+        _need(sink, "sink", torch.float32, (n_heads,))
+    pk = pv = pt = None
+    if pool:
+        pk, pv, pt = pooled
+        _need(pk, "pk_pages", q.dtype, (None, n_kv, page, d))
+        _need(pv, "pv_pages", q.dtype, (None, n_kv, page, dv))
+        _need(pt, "pool_table", torch.int32)
+    lib = pool_attention_prefill_lib(d, dv, n_heads // n_kv, page)
+    _ok(lib.dryft_pool_attn_prefill(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.shape[1], page, _ptr(pk),
+                                    _ptr(pv), _ptr(pt), pt.shape[1] if pt is not None else 0, _ptr(sink), _ptr(tile_tok0),
+                                    _ptr(tile_rows), _ptr(tok_slot), _ptr(tok_pos), _ptr(out), int(n_tiles), n_heads, n_kv,
+                                    float(scale), int(size), int(pool), _stream()),
+        f"pool_attn_prefill (window {size}, blocks of {pool})")
 
 
 def pool_attn_prep(proj, q_bias, k_bias, v_bias, inv_freq, inv_freq_lo, rot: int, tok_slot, tok_pos, q_out, k_pages, v_pages,

@@ -100,6 +100,8 @@ class PooledWindowAttention:
         self.rot = int(getattr(self.position, "rotary_dim", 0) or 0) if getattr(self.position, "inv_freq", None) is not None else 0
         K.pool_attention_lib(self.qk_dim, self.v_dim, self.group)   # build (or find) the kernels of this head shape now
         self.use_prefill_kernel = rt.is_bf16 and K.pool_attention_prefill_supported(self.qk_dim, self.v_dim, self.group)
+        if self.use_prefill_kernel:
+            K.pool_attention_prefill_lib(self.qk_dim, self.v_dim, self.group)
 
     def kv_need(self) -> Optional[KVNeed]:
         if self.size >= NO_WINDOW:
@@ -136,7 +138,7 @@ class PooledWindowAttention:
                 K.pool_attn_blocks(cache.k, cache.v, cache.page_table, pc.k, pc.v, pc.page_table, ctx.tok_slot, ctx.tok_pos, n,
                                    self.pool, self.group)
         o = torch.empty((n, self.n_heads, self.v_dim), dtype=h.dtype, device=dev)
-        if self.use_prefill_kernel and not ctx.decode and ctx.n_tiles > 0:
+        if self.use_prefill_kernel and not ctx.decode and ctx.n_tiles > 0 and cache.k.shape[2] == 64:
             K.pool_attn_prefill(q, cache.k, cache.v, cache.page_table, pooled, self.sink, ctx.tile_tok0, ctx.tile_rows, ctx.tok_slot,
                                 ctx.tok_pos, o, ctx.n_tiles, self.scale, self.size, self.pool)
         else:

@@ -13,7 +13,8 @@ With ``inner = heads * v_dim``, ``N = state`` and ``G = groups``, one product of
                  the ``inner`` values (each part by its own root mean square, ``eps`` inside the root)
 
 The matrix state and the convolution's last ``taps - 1`` inputs are per-sequence state of fixed size (32-bit, zero when a
-sequence starts), so a prompt, a piece of one and a single token are the same operation (``csrc/ssm.cu``).  The product's
+sequence starts), so a prompt, a piece of one and a single token are the same operation (``csrc/ssm.cu``); a step of many
+tokens runs its chunks side by side (each from a zero state, a prefix over the chunks' states, then each from its start state).  The product's
 result is kept in 32-bit and everything behind it up to the norm's output runs in 32-bit in both precisions.
 ``params["names"]`` maps the tensors' roles to their names behind the prefix.
 """
@@ -76,6 +77,7 @@ class SSD:
         f32 = lambda role: weights.load(nm[role], "vector").to(torch.float32).contiguous()
         self.conv_w, self.conv_b = f32("conv"), f32("conv_bias")
         self.dt_bias, self.a_log, self.d_skip, self.norm_w = f32("dt_bias"), f32("a_log"), f32("d"), f32("norm")
+        self.chunked_from = int(params.get("chunked_from", 4 * K.SSM_CHUNK_TOKENS))   # steps of fewer tokens walk them in order
         K.ssm_lib()
         K.rowops_lib()
 
@@ -95,7 +97,8 @@ class SSD:
         K.ssm_conv(proj, self.inner, self.conv_w, self.conv_b, ctx.cu_q, ctx.seq_slot, ctx.n_seqs, state.get("tail"), xbc)
         y = torch.empty((n, self.inner), dtype=torch.float32, device=dev)
         K.ssm_scan(xbc, proj, self.inner + self.channels, self.dt_bias, self.a_log, self.d_skip, ctx.cu_q, ctx.seq_slot, ctx.n_seqs,
-                   self.heads, self.groups, self.n_state, self.v_dim, state["s"], y)
+                   self.heads, self.groups, self.n_state, self.v_dim, state["s"], y,
+                   chunked=not ctx.decode and n >= self.chunked_from)
         out = torch.empty((n, self.inner), dtype=h.dtype, device=dev)
         K.gated_group_norm(y, proj[:, :self.inner], self.norm_w, self.parts, self.eps, out)
         return linear(out, self.w_o, self.rt)

@@ -4,6 +4,8 @@ tokens, unequal batches against each request alone, slots and pages used again (
 block and page edges, the first tokens, the stream after every layer, greedy generation through ``Engine.generate`` /
 ``generate_many`` (captured graphs and eager), the replay program and the command line as child processes."""
 
+import math
+
 import numpy as np
 import pytest
 import torch
@@ -40,6 +42,18 @@ def engine(entry, dtype, **kw):
     opts = dict(dtype=dtype, max_batch=8, max_seq_len=512, max_tokens=2048, cuda_graphs=False)
     opts.update(kw)
     return Engine(entry[2], EngineOptions(**opts))
+
+
+def limits(entry):
+    """The bfloat16 limits of this model, from what rounding alone does to a prompt of its own under the plain evaluation."""
+    cfg, tensors, _, memo = entry
+    if "limits" not in memo:
+        memo["limits"] = M.bf16_limits(cfg, tensors, M.prompts(cfg, [120], seed=77)[0])
+    return memo["limits"]
+
+
+def check(entry, got, want, dtype, what):
+    M.assert_close(got, want, dtype, what, limits(entry) if dtype != "float32" else None)
 
 
 def close_all(entry, pairs, dtype, what):
@@ -344,3 +358,107 @@ def test_configurations_drawn_at_random(tmp_path, seed):
             e = M.row_errors(got_all, torch.cat([w for _, w, _ in pairs]))
             assert float(e.median()) <= limits(entry)[0], f"{what}: median row off by {float(e.median()):.3g}"
         eng.cache.check()
+
+
+@pytest.mark.parametrize("size, pool, d, dv, group", [(20, 4, 32, 16, 2), (64, 16, 16, 48, 1), (130, 64, 64, 64, 4), (7, 1, 16, 16, 3),
+                                                       (5, 12, 32, 32, 2), (1, 1, 16, 16, 1), (1000, 8, 16, 32, 2)])
+def test_prompt_kernel_against_the_row_kernel(size, pool, d, dv, group):
+    """The tensor-core prompt kernel (bfloat16) against the row-wise kernel in 32-bit on the same cache: whole prompts and
+    later portions of one, over shuffled pages whose unused rows are poisoned, with scores spread widely so that a key
+    wrongly seen or missed at a window's or a block's edge moves whole rows."""
+    from dryft_b200.ops import kernels as K
+
+    if not K.pool_attention_prefill_supported(d, dv, group):
+        pytest.skip("no prompt kernel for this head shape")
+    torch.manual_seed(size * 31 + pool)
+    dev, page, n_kv = "cuda", 64, 2
+    H = n_kv * group
+    seqs = [(0, 200), (37, 181), (0, 1), (128, 330), (63, 66)]              # (first position of this step, length so far)
+    max_pages = 8
+    n_pages = len(seqs) * max_pages
+    perm = torch.randperm(n_pages)
+    table = perm.view(len(seqs), max_pages).to(torch.int32).to(dev)
+    ptable = torch.randperm(n_pages).view(len(seqs), max_pages).to(torch.int32).to(dev)
+    k32 = torch.full((n_pages, n_kv, page, d), float("nan"), device=dev)
+    v32 = torch.full((n_pages, n_kv, page, dv), float("nan"), device=dev)
+    pk32, pv32 = torch.full_like(k32, float("nan")), torch.full_like(v32, float("nan"))
+    slots, poss, t0s, tns = [], [], [], []
+    for s, (start, length) in enumerate(seqs):
+        kk = torch.randn(length, n_kv, d).to(torch.bfloat16).float().to(dev)
+        vv = torch.randn(length, n_kv, dv).to(torch.bfloat16).float().to(dev)
+        for j in range(length):
+            k32[table[s, j // page], :, j % page] = kk[j]
+            v32[table[s, j // page], :, j % page] = vv[j]
+        for b in range(length // pool):
+            pk32[ptable[s, b // page], :, b % page] = kk[b * pool:(b + 1) * pool].mean(0).to(torch.bfloat16).float()
+            pv32[ptable[s, b // page], :, b % page] = vv[b * pool:(b + 1) * pool].mean(0).to(torch.bfloat16).float()
+        for q0 in range(start, length, 64):
+            t0s.append(len(slots) + q0 - start)
+            tns.append(min(64, length - q0))
+        slots += [s] * (length - start)
+        poss += list(range(start, length))
+    n = len(slots)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    tok_slot, tok_pos, tile0, tilen = i32(slots), i32(poss), i32(t0s), i32(tns)
+    q32 = torch.randn(n, H, d, device=dev).to(torch.bfloat16).float()
+    sink = torch.randn(H, device=dev) * 2.0
+    scale = 6.0 / math.sqrt(d)
+    want = torch.empty(n, H, dv, device=dev)
+    K.pool_attn_rows(q32, k32, v32, table, (pk32, pv32, ptable), sink, tok_slot, tok_pos, want, scale, size, pool)
+    got = torch.empty(n, H, dv, device=dev, dtype=torch.bfloat16)
+    bf = lambda x: x.to(torch.bfloat16)
+    K.pool_attn_prefill(bf(q32), bf(k32), bf(v32), table, (bf(pk32), bf(pv32), ptable), sink, tile0, tilen, tok_slot, tok_pos, got,
+                        len(t0s), scale, size, pool)
+    torch.cuda.synchronize()
+    assert torch.isfinite(want).all() and torch.isfinite(got.float()).all()
+    err = (got.float() - want).abs().amax(dim=(1, 2))
+    assert float(err.max()) <= 0.03, f"token {int(err.argmax())} (slot {slots[int(err.argmax())]}, position {poss[int(err.argmax())]}) off by {float(err.max()):.3g}"
+    # without a sink and without blocks the same kernel is a plain sliding window
+    K.pool_attn_rows(q32, k32, v32, table, None, None, tok_slot, tok_pos, want, scale, size, 0)
+    K.pool_attn_prefill(bf(q32), bf(k32), bf(v32), table, None, None, tile0, tilen, tok_slot, tok_pos, got, len(t0s), scale, size, 0)
+    torch.cuda.synchronize()
+    assert float((got.float() - want).abs().max()) <= 0.03
+
+
+@pytest.mark.parametrize("name", ["ssm_sizes", "mixed"])
+def test_many_token_steps_of_the_state_space_mixer_run_in_chunks(tmp_path_factory, monkeypatch, name):
+    """Steps of many tokens cut into chunks that run side by side (here chunks of 16 tokens, from steps of 2 tokens on):
+    whole prompts, pieces that continue a sequence at odd places, unequal batches with a single-token request, 32-bit."""
+    from dryft_b200.ops import kernels as K
+    from dryft_b200.parts.ssd import SSD
+
+    monkeypatch.setattr(K, "SSM_CHUNK_TOKENS", 16)
+    entry = model(name, tmp_path_factory)
+    cfg = entry[0]
+    eng = engine(entry, "float32")
+    n_ssd = 0
+    for blk in eng.model.blocks:
+        if isinstance(blk.mixer, SSD):
+            blk.mixer.chunked_from = 2
+            n_ssd += 1
+    assert n_ssd
+    reqs = M.prompts(cfg, [200, 131, 1, 47, 16, 33], seed=12)
+    n0 = K.launch_count
+    with torch.inference_mode():
+        for portion in (200, 97, 16, 5):
+            toks = reqs[0]
+            s = eng.cache.open_sequences(1)
+            rows = []
+            for c0 in range(0, len(toks), portion):
+                piece = toks[c0:c0 + portion]
+                rows.append(eng.stepper.step(s, [piece], [list(range(len(piece)))]))
+            eng.cache.close_sequences(s)
+            check(entry, torch.cat(rows), plain_logits(entry, toks), "float32", f"{name} in chunks, portions of {portion}")
+        slots = eng.cache.open_sequences(len(reqs))
+        heads = [max(1, len(t) - 3) for t in reqs]
+        got = eng.stepper.step(slots, [t[:h] for t, h in zip(reqs, heads)], [list(range(h)) for h in heads])
+        at, pairs = 0, []
+        for t, h in zip(reqs, heads):
+            pairs.append((got[at:at + h], plain_logits(entry, t)[:h], f"prompt of {h}"))
+            at += h
+        close_all(entry, pairs, "float32", f"{name} in chunks, batched prompts")
+        rows = decode_together(eng, slots, reqs, heads)
+        close_all(entry, [(torch.cat(r), plain_logits(entry, reqs[b])[heads[b]:], f"request {b}") for b, r in rows.items() if r],
+                  "float32", f"{name} decoding behind chunked prompts")
+    assert K.launch_count > n0
+    eng.cache.check()
