@@ -30,6 +30,7 @@ namespace {
 constexpr int D = DRYFT_QK_DIM, DV = DRYFT_V_DIM, REP = DRYFT_GROUP;
 constexpr int DR = (D + 31) / 32, DVR = (DV + 31) / 32;
 constexpr int ROWS_WARPS = 4;
+constexpr int BLOCKS_THREADS = (D + DV + 31) / 32 * 32 < 1024 ? (D + DV + 31) / 32 * 32 : 1024;   // a thread a column of a key or a value
 constexpr int PREP_WARPS = 4;
 
 // sin and cos of  pos * (f_hi + f_lo): the product is formed in 32-bit, and what its rounding drops (recovered exactly with
@@ -115,7 +116,7 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) pool_attn_prep_kernel(
 }
 
 template <typename T>
-__global__ void __launch_bounds__(128) pool_attn_blocks_kernel(
+__global__ void __launch_bounds__(BLOCKS_THREADS) pool_attn_blocks_kernel(
     const T* __restrict__ k_pages, const T* __restrict__ v_pages, const int* __restrict__ page_table, int max_pages, int page_size,
     T* __restrict__ pk_pages, T* __restrict__ pv_pages, const int* __restrict__ pool_table, int pool_max_pages,
     const int* __restrict__ tok_slot, const int* __restrict__ tok_pos, int G, int P) {
@@ -130,7 +131,8 @@ __global__ void __launch_bounds__(128) pool_attn_blocks_kernel(
   const float inv = 1.f / (float)P;
   for (int c = threadIdx.x; c < D + DV; c += blockDim.x) {
     float acc = 0.f;
-    for (int j = 0; j < P; ++j) {
+#pragma unroll 8
+    for (int j = 0; j < P; ++j) {   // rows in order: the sum does not depend on how the loads are scheduled
       const int pj = p0 + j;
       const int page = page_table[(size_t)slot * max_pages + pj / page_size];
       const size_t r = ((size_t)page * G + g) * page_size + pj % page_size;
@@ -368,11 +370,11 @@ DRYFT_API int dryft_pool_attn_blocks(int is_bf16, const void* k_pages, const voi
   if (G < 1 || G > 65535 || page_size < 1) return DRYFT_ERR_UNSUPPORTED;
   dim3 grid(n, G);
   if (is_bf16)
-    pool_attn_blocks_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table,
+    pool_attn_blocks_kernel<__nv_bfloat16><<<grid, BLOCKS_THREADS, 0, st>>>((const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table,
                                                                  max_pages, page_size, (__nv_bfloat16*)pk, (__nv_bfloat16*)pv, pool_table,
                                                                  pool_max_pages, tok_slot, tok_pos, G, P);
   else
-    pool_attn_blocks_kernel<float><<<grid, 128, 0, st>>>((const float*)k_pages, (const float*)v_pages, page_table, max_pages, page_size,
+    pool_attn_blocks_kernel<float><<<grid, BLOCKS_THREADS, 0, st>>>((const float*)k_pages, (const float*)v_pages, page_table, max_pages, page_size,
                                                          (float*)pk, (float*)pv, pool_table, pool_max_pages, tok_slot, tok_pos, G, P);
   return launch_status();
 }

@@ -11,8 +11,8 @@
 // one and a single token are the same operation.
 //
 //   ssm_conv    out[t, c] = silu(cb[c] + sum_j cw[c, j] * in[t - (taps - 1) + j, c]); inputs before the step's first
-//               token come from the tail (zeros before the sequence's start).  One block per token.
-//   ssm_tail    the tail after the step (run after ssm_conv, which reads the old one).  One block per sequence.
+//               token come from the tail (zeros before the sequence's start).  A thread a (token, channel).
+//   ssm_tail    the tail after the step (run after ssm_conv, which reads the old one).  A thread a (sequence, channel).
 //   ssm_scan    one block per (sequence, head, slice of WARPS value columns); a warp owns one column p of S, a lane the
 //               rows n = lane, lane + 32, ...; tokens in order, the next token's operands requested before the current
 //               token's arithmetic; y_t[p] is a warp sum.
@@ -49,7 +49,8 @@ __global__ void __launch_bounds__(CONV_THREADS) ssm_conv_kernel(
   const int slot = seq_slot[b];
   if (slot < 0) return;
   const int i = t - cu_q[b];          // index of the token within this step's part of its sequence
-  for (int c = threadIdx.x; c < CH; c += CONV_THREADS) {
+  const int c = blockIdx.y * CONV_THREADS + threadIdx.x;
+  if (c < CH) {
     float acc = cb[c];
     for (int j = 0; j < taps; ++j) {
       const int back = taps - 1 - j, src = i - back;
@@ -70,7 +71,8 @@ __global__ void __launch_bounds__(CONV_THREADS) ssm_tail_kernel(
   const int t0 = cu_q[b], q = cu_q[b + 1] - t0;
   if (q <= 0) return;
   float* tl = tail + (size_t)slot * (taps - 1) * CH;
-  for (int c = threadIdx.x; c < CH; c += CONV_THREADS) {
+  const int c = blockIdx.y * CONV_THREADS + threadIdx.x;
+  if (c < CH) {
     // ascending k: an old entry is read at k + q > k, before it is overwritten
     for (int k = 0; k < taps - 1; ++k) {
       const int src = q - (taps - 1) + k;
@@ -196,10 +198,12 @@ DRYFT_API int dryft_ssm_conv(const float* proj, int ld, int x_off, int CH, const
                              const float* cw, const float* cb, int taps, float* tail, float* out, int n_tokens, cudaStream_t st) {
   if (n_tokens <= 0 || n_seqs <= 0) return 0;
   if (taps < 1 || taps > MAX_TAPS || CH < 1 || (taps > 1 && tail == nullptr)) return DRYFT_ERR_UNSUPPORTED;
-  ssm_conv_kernel<<<n_tokens, CONV_THREADS, 0, st>>>(proj, ld, x_off, CH, cu_q, seq_slot, n_seqs, cw, cb, taps, tail, out);
+  const dim3 grid_c(n_tokens, (CH + CONV_THREADS - 1) / CONV_THREADS), grid_t(n_seqs, (CH + CONV_THREADS - 1) / CONV_THREADS);
+  if (grid_c.y > 65535) return DRYFT_ERR_UNSUPPORTED;
+  ssm_conv_kernel<<<grid_c, CONV_THREADS, 0, st>>>(proj, ld, x_off, CH, cu_q, seq_slot, n_seqs, cw, cb, taps, tail, out);
   int rc = launch_status();
   if (rc || taps == 1) return rc;
-  ssm_tail_kernel<<<n_seqs, CONV_THREADS, 0, st>>>(proj, ld, x_off, CH, cu_q, seq_slot, taps, tail);
+  ssm_tail_kernel<<<grid_t, CONV_THREADS, 0, st>>>(proj, ld, x_off, CH, cu_q, seq_slot, taps, tail);
   return launch_status();
 }
 

@@ -462,3 +462,59 @@ def test_many_token_steps_of_the_state_space_mixer_run_in_chunks(tmp_path_factor
                   "float32", f"{name} decoding behind chunked prompts")
     assert K.launch_count > n0
     eng.cache.check()
+
+
+@pytest.mark.parametrize("size, pool, far", [(50, 8, 13), (64, 64, 100), (129, 5, 3), (3, 7, 640)])
+def test_one_key_that_stands_out_at_every_edge(size, pool, far):
+    """Both attention kernels (row-wise in 32-bit, prompts in bfloat16) against the plain function over 700 tokens in which ONE
+    key, at position ``far``, outweighs all others for every query: it is seen while in the window, not at all between the
+    window and its block's completion, and as a 1 / pool share of its block's row from then on (hundreds of tokens later too)."""
+    from dryft_b200.ops import kernels as K
+
+    torch.manual_seed(far)
+    dev, page, n_kv, group, d, dv, L = "cuda", 64, 1, 2, 16, 16, 700
+    H = n_kv * group
+    k = (0.1 * torch.randn(L, n_kv, d)).to(torch.bfloat16).double()
+    v = torch.randn(L, n_kv, dv).to(torch.bfloat16).double()
+    q = torch.zeros(L, H, d, dtype=torch.float64)
+    q[:, :, 3] = 1.0
+    k[far, 0, 3] = 40.0                       # its score leads by 40 * scale; in its block's mean by 40 * scale / pool
+    v[far, 0] = 7.0
+    sink = torch.tensor([-1.0, 2.0], dtype=torch.float64)
+    scale = 1.5
+    want = P.pooled_window_attention(q, k, v, sink, scale, size, pool)
+    n_pages = 12
+    table = torch.randperm(n_pages)[None].to(torch.int32).to(dev)
+    ptable = torch.randperm(n_pages)[None].to(torch.int32).to(dev)
+    k32 = torch.full((n_pages, n_kv, page, d), float("nan"), device=dev)
+    v32 = torch.full((n_pages, n_kv, page, dv), float("nan"), device=dev)
+    pk32, pv32 = torch.full_like(k32, float("nan")), torch.full_like(v32, float("nan"))
+    for j in range(L):
+        k32[table[0, j // page], :, j % page] = k[j].float().to(dev)
+        v32[table[0, j // page], :, j % page] = v[j].float().to(dev)
+    for b in range(L // pool):
+        pk32[ptable[0, b // page], :, b % page] = k[b * pool:(b + 1) * pool].mean(0).float().to(dev)
+        pv32[ptable[0, b // page], :, b % page] = v[b * pool:(b + 1) * pool].mean(0).float().to(dev)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    tok_slot, tok_pos = i32([0] * L), i32(list(range(L)))
+    got = torch.empty(L, H, dv, device=dev)
+    for splits in (1, 3):
+        po = torch.empty(L, H, splits, dv, device=dev) if splits > 1 else None
+        pm = torch.empty(L, H, splits, 2, device=dev) if splits > 1 else None
+        K.pool_attn_rows(q.float().to(dev), k32, v32, table, (pk32, pv32, ptable), sink.float().to(dev), tok_slot, tok_pos, got, scale,
+                         size, pool, splits, po, pm)
+        err = (got.double().cpu() - want).abs().amax(dim=(1, 2))
+        assert float(err.max()) <= 2e-5, f"{splits} split(s): position {int(err.argmax())} off by {float(err.max()):.3g}"
+    # the plain function itself shows the three regimes (the test's inputs are made for it)
+    first_block_seen = (far // pool) * pool + pool - 1 + size
+    assert float(want[min(far + size - 1, L - 1), 0, 0]) > 6.0
+    if far + size < min(first_block_seen, L):
+        assert abs(float(want[far + size, 0, 0])) < 3.0
+    if d % 16 == 0 and first_block_seen < L:
+        bf = lambda x: x.to(torch.bfloat16)
+        t0 = list(range(0, L, 64))
+        gotb = torch.empty(L, H, dv, device=dev, dtype=torch.bfloat16)
+        K.pool_attn_prefill(bf(q.float().to(dev)), bf(k32), bf(v32), table, (bf(pk32), bf(pv32), ptable), sink.float().to(dev), i32(t0),
+                            i32([min(64, L - a) for a in t0]), tok_slot, tok_pos, gotb, len(t0), scale, size, pool)
+        errb = (gotb.double().cpu() - want).abs().amax(dim=(1, 2))
+        assert float(errb.max()) <= 0.06, f"prompt kernel: position {int(errb.argmax())} off by {float(errb.max()):.3g}"
