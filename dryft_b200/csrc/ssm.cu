@@ -13,7 +13,7 @@
 //   ssm_conv    out[t, c] = silu(cb[c] + sum_j cw[c, j] * in[t - (taps - 1) + j, c]); inputs before the step's first
 //               token come from the tail (zeros before the sequence's start).  A thread a (token, channel).
 //   ssm_tail    the tail after the step (run after ssm_conv, which reads the old one).  A thread a (sequence, channel).
-//   ssm_scan    one block per (sequence, head, slice of WARPS value columns); a warp owns one column p of S, a lane the
+//   ssm_scan    one block per (sequence, head, slice of WARPS x COLS value columns); a warp owns COLS columns of S, a lane the
 //               rows n = lane, lane + 32, ...; tokens in order, the next token's operands requested before the current
 //               token's arithmetic; y_t[p] is a warp sum.
 //   chunked     a step of many tokens is cut into chunks of `cht` tokens that run side by side, in three launches: (1) every
@@ -28,7 +28,8 @@
 namespace {
 constexpr int CONV_THREADS = 128;
 constexpr int SCAN_WARPS = 4;
-constexpr int MAX_NR = 8;      // state rows a lane holds: N <= 256
+constexpr int MAX_NR = 8;      // state rows a lane holds at most: N <= 256
+constexpr int COLS = 4;        // value columns of the state a warp owns
 constexpr int MAX_TAPS = 16;
 
 __device__ __forceinline__ int seq_of(const int* __restrict__ cu_q, int n_seqs, int t) {
@@ -97,7 +98,9 @@ __device__ __forceinline__ bool chunk_of(const int* __restrict__ cu_q, int n_seq
 // MODE 0: block x = sequence; its tokens in order from the slot's state, which is left advanced.
 // MODE 1: block x = chunk; from a zero state; leaves the chunk's own state in cstate[chunk] and its decays' product in cdec.
 // MODE 2: block x = chunk; from the start state in cstate[chunk]; writes y.
-template <int MODE>
+// A warp owns COLS neighbouring value columns of S (B_t and C_t, once in registers, serve all of them); a lane the rows
+// n = lane, lane + 32, ... (NR of them: N <= 32 NR).
+template <int MODE, int NR>
 __global__ void __launch_bounds__(SCAN_WARPS * 32) ssm_scan_kernel(
     const float* __restrict__ xbc, int CH, const float* __restrict__ proj, int ld, int dt_off, const float* __restrict__ dt_bias,
     const float* __restrict__ a_log, const float* __restrict__ Dp, const int* __restrict__ cu_q, const int* __restrict__ seq_slot,
@@ -105,69 +108,86 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) ssm_scan_kernel(
     float* __restrict__ cdec, float* __restrict__ y) {
   const int hd = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int p = blockIdx.z * SCAN_WARPS + warp;
+  const int p0 = (blockIdx.z * SCAN_WARPS + warp) * COLS;
   int b = blockIdx.x, c = 0;
   if (MODE != 0 && !chunk_of(cu_q, n_seqs, cht, blockIdx.x, &b, &c)) return;
   const int slot = seq_slot[b];
-  if (slot < 0 || p >= dv) return;
+  if (slot < 0 || p0 >= dv) return;
   int t0 = cu_q[b], t1 = cu_q[b + 1];
   if (MODE != 0) { t0 += c * cht; t1 = min(t1, t0 + cht); }
   if (t1 <= t0) return;
   const int inner = heads * dv, g = hd / (heads / groups);
-  const int xo = hd * dv + p, bo = inner + g * N, co = inner + groups * N + g * N;
+  const int xo = hd * dv + p0, bo = inner + g * N, co = inner + groups * N + g * N;
   const float rate = expf(a_log[hd]), bias = dt_bias[hd], dskip = Dp[hd];
-  float* sp = MODE == 0 ? state + (((size_t)slot * heads + hd) * N) * dv + p
-                        : cstate + (((size_t)blockIdx.x * heads + hd) * N) * dv + p;
-  float S[MAX_NR];
+  float* sp = MODE == 0 ? state + (((size_t)slot * heads + hd) * N) * dv + p0
+                        : cstate + (((size_t)blockIdx.x * heads + hd) * N) * dv + p0;
+  float S[NR][COLS];
 #pragma unroll
-  for (int r = 0; r < MAX_NR; ++r) {
+  for (int r = 0; r < NR; ++r) {
     const int n = lane + 32 * r;
-    S[r] = (MODE != 1 && n < N) ? sp[(size_t)n * dv] : 0.f;
+#pragma unroll
+    for (int j = 0; j < COLS; ++j) S[r][j] = (MODE != 1 && n < N && p0 + j < dv) ? sp[(size_t)n * dv + j] : 0.f;
   }
   float dprod = 1.f;
-  float Bn[MAX_NR], Cn[MAX_NR], xv, dtr;
+  float Bn[NR], Cn[NR], xv[COLS], dtr;
   auto fetch = [&](int t) {
     const float* row = xbc + (size_t)t * CH;
 #pragma unroll
-    for (int r = 0; r < MAX_NR; ++r) {
+    for (int r = 0; r < NR; ++r) {
       const int n = lane + 32 * r;
       Bn[r] = n < N ? row[bo + n] : 0.f;
       Cn[r] = n < N ? row[co + n] : 0.f;
     }
-    xv = row[xo];
+#pragma unroll
+    for (int j = 0; j < COLS; ++j) xv[j] = p0 + j < dv ? row[xo + j] : 0.f;
     dtr = proj[(size_t)t * ld + dt_off + hd];
   };
   fetch(t0);
   for (int t = t0; t < t1; ++t) {
-    float Bc[MAX_NR], Cc[MAX_NR];
+    float Bc[NR], Cc[NR], dx[COLS], x[COLS];
 #pragma unroll
-    for (int r = 0; r < MAX_NR; ++r) { Bc[r] = Bn[r]; Cc[r] = Cn[r]; }
-    const float x = xv, dt = softplusf_(dtr + bias);
+    for (int r = 0; r < NR; ++r) { Bc[r] = Bn[r]; Cc[r] = Cn[r]; }
+    const float dt = softplusf_(dtr + bias);
+#pragma unroll
+    for (int j = 0; j < COLS; ++j) { x[j] = xv[j]; dx[j] = dt * xv[j]; }
     if (t + 1 < t1) fetch(t + 1);
-    const float decay = expf(-rate * dt), dx = dt * x;
+    const float decay = expf(-rate * dt);
     if (MODE == 1) {
       dprod *= decay;
 #pragma unroll
-      for (int r = 0; r < MAX_NR; ++r) S[r] = fmaf(decay, S[r], Bc[r] * dx);
-    } else {
-      float acc = 0.f;
+      for (int r = 0; r < NR; ++r)
 #pragma unroll
-      for (int r = 0; r < MAX_NR; ++r) {
-        S[r] = fmaf(decay, S[r], Bc[r] * dx);
-        acc = fmaf(S[r], Cc[r], acc);
+        for (int j = 0; j < COLS; ++j) S[r][j] = fmaf(decay, S[r][j], Bc[r] * dx[j]);
+    } else {
+      float acc[COLS];
+#pragma unroll
+      for (int j = 0; j < COLS; ++j) acc[j] = 0.f;
+#pragma unroll
+      for (int r = 0; r < NR; ++r)
+#pragma unroll
+        for (int j = 0; j < COLS; ++j) {
+          S[r][j] = fmaf(decay, S[r][j], Bc[r] * dx[j]);
+          acc[j] = fmaf(S[r][j], Cc[r], acc[j]);
+        }
+      float mine = 0.f, xm = 0.f;      // lane j keeps column j's sum
+#pragma unroll
+      for (int j = 0; j < COLS; ++j) {
+        const float sj = warp_sum(acc[j]);
+        if (lane == j) { mine = sj; xm = x[j]; }
       }
-      acc = warp_sum(acc);
-      if (lane == 0) y[(size_t)t * inner + xo] = fmaf(dskip, x, acc);
+      if (lane < COLS && p0 + lane < dv) y[(size_t)t * inner + xo + lane] = fmaf(dskip, xm, mine);
     }
   }
   if (MODE != 2) {
 #pragma unroll
-    for (int r = 0; r < MAX_NR; ++r) {
+    for (int r = 0; r < NR; ++r) {
       const int n = lane + 32 * r;
-      if (n < N) sp[(size_t)n * dv] = S[r];
+#pragma unroll
+      for (int j = 0; j < COLS; ++j)
+        if (n < N && p0 + j < dv) sp[(size_t)n * dv + j] = S[r][j];
     }
   }
-  if (MODE == 1 && p == 0 && lane == 0) cdec[(size_t)blockIdx.x * heads + hd] = dprod;
+  if (MODE == 1 && p0 == 0 && lane == 0) cdec[(size_t)blockIdx.x * heads + hd] = dprod;
 }
 
 // S_start(c + 1) = decay(c) S_start(c) + S_own(c) over a sequence's chunks, from the slot's state; cstate[c] turns from the
@@ -184,11 +204,18 @@ __global__ void __launch_bounds__(256) ssm_chunk_prefix_kernel(const int* __rest
   const int nc = (cu_q[b + 1] - cu_q[b] + cht - 1) / cht;
   float* sp = state + ((size_t)slot * heads + hd) * per_head + e;
   float carry = *sp;
-  for (int c = 0; c < nc; ++c) {
-    float* cs = cstate + ((size_t)(base + c) * heads + hd) * per_head + e;
-    const float own = *cs;
+  const size_t step = (size_t)heads * per_head;
+  float* cs = cstate + ((size_t)base * heads + hd) * per_head + e;
+  const float* dp = cdec + (size_t)base * heads + hd;
+  float own = nc > 0 ? *cs : 0.f, dec = nc > 0 ? *dp : 0.f;
+  for (int c = 0; c < nc; ++c) {     // the next chunk's values are requested before this chunk's store
+    const float own_next = c + 1 < nc ? cs[step] : 0.f, dec_next = c + 1 < nc ? dp[heads] : 0.f;
     *cs = carry;
-    carry = fmaf(cdec[(size_t)(base + c) * heads + hd], carry, own);
+    carry = fmaf(dec, carry, own);
+    own = own_next;
+    dec = dec_next;
+    cs += step;
+    dp += heads;
   }
   *sp = carry;
 }
@@ -207,15 +234,32 @@ DRYFT_API int dryft_ssm_conv(const float* proj, int ld, int x_off, int CH, const
   return launch_status();
 }
 
+namespace {
+template <int MODE>
+void launch_scan(dim3 grid, cudaStream_t st, const float* xbc, int CH, const float* proj, int ld, int dt_off, const float* dt_bias,
+                 const float* a_log, const float* Dp, const int* cu_q, const int* seq_slot, int n_seqs, int cht, int heads, int groups,
+                 int N, int dv, float* state, float* cstate, float* cdec, float* y) {
+#define DRYFT_SCAN(NR)                                                                                                         \
+  ssm_scan_kernel<MODE, NR><<<grid, SCAN_WARPS * 32, 0, st>>>(xbc, CH, proj, ld, dt_off, dt_bias, a_log, Dp, cu_q, seq_slot, n_seqs, \
+                                                             cht, heads, groups, N, dv, state, cstate, cdec, y)
+  const int nr = (N + 31) / 32;
+  if (nr <= 1) DRYFT_SCAN(1);
+  else if (nr <= 2) DRYFT_SCAN(2);
+  else if (nr <= 4) DRYFT_SCAN(4);
+  else DRYFT_SCAN(8);
+#undef DRYFT_SCAN
+}
+}  // namespace
+
 DRYFT_API int dryft_ssm_scan(const float* xbc, int CH, const float* proj, int ld, int dt_off, const float* dt_bias, const float* a_log,
                              const float* Dp, const int* cu_q, const int* seq_slot, int n_seqs, int heads, int groups, int N, int dv,
                              float* state, float* y, cudaStream_t st) {
   if (n_seqs <= 0) return 0;
   if (heads < 1 || groups < 1 || heads % groups || N < 1 || N > 32 * MAX_NR || dv < 1 || heads > 65535) return DRYFT_ERR_UNSUPPORTED;
-  dim3 grid(n_seqs, heads, (dv + SCAN_WARPS - 1) / SCAN_WARPS);
+  dim3 grid(n_seqs, heads, (dv + SCAN_WARPS * COLS - 1) / (SCAN_WARPS * COLS));
   if (grid.z > 65535) return DRYFT_ERR_UNSUPPORTED;
-  ssm_scan_kernel<0><<<grid, SCAN_WARPS * 32, 0, st>>>(xbc, CH, proj, ld, dt_off, dt_bias, a_log, Dp, cu_q, seq_slot, n_seqs, 0, heads,
-                                                      groups, N, dv, state, nullptr, nullptr, y);
+  launch_scan<0>(grid, st, xbc, CH, proj, ld, dt_off, dt_bias, a_log, Dp, cu_q, seq_slot, n_seqs, 0, heads, groups, N, dv, state, nullptr,
+                 nullptr, y);
   return launch_status();
 }
 
@@ -228,18 +272,18 @@ DRYFT_API int dryft_ssm_scan_chunked(const float* xbc, int CH, const float* proj
   if (n_seqs <= 0 || n_chunks <= 0) return 0;
   if (heads < 1 || groups < 1 || heads % groups || N < 1 || N > 32 * MAX_NR || dv < 1 || heads > 65535 || cht < 1 || n_seqs > 65535)
     return DRYFT_ERR_UNSUPPORTED;
-  dim3 grid(n_chunks, heads, (dv + SCAN_WARPS - 1) / SCAN_WARPS);
+  dim3 grid(n_chunks, heads, (dv + SCAN_WARPS * COLS - 1) / (SCAN_WARPS * COLS));
   const int per_head = N * dv;
   dim3 grid_b(n_seqs, heads, (per_head + 255) / 256);
   if (grid.z > 65535 || grid_b.z > 65535) return DRYFT_ERR_UNSUPPORTED;
-  ssm_scan_kernel<1><<<grid, SCAN_WARPS * 32, 0, st>>>(xbc, CH, proj, ld, dt_off, dt_bias, a_log, Dp, cu_q, seq_slot, n_seqs, cht, heads,
-                                                      groups, N, dv, state, cstate, cdec, y);
+  launch_scan<1>(grid, st, xbc, CH, proj, ld, dt_off, dt_bias, a_log, Dp, cu_q, seq_slot, n_seqs, cht, heads, groups, N, dv, state, cstate,
+                 cdec, y);
   int rc = launch_status();
   if (rc) return rc;
   ssm_chunk_prefix_kernel<<<grid_b, 256, 0, st>>>(cu_q, seq_slot, cht, heads, per_head, state, cstate, cdec);
   rc = launch_status();
   if (rc) return rc;
-  ssm_scan_kernel<2><<<grid, SCAN_WARPS * 32, 0, st>>>(xbc, CH, proj, ld, dt_off, dt_bias, a_log, Dp, cu_q, seq_slot, n_seqs, cht, heads,
-                                                      groups, N, dv, state, cstate, cdec, y);
+  launch_scan<2>(grid, st, xbc, CH, proj, ld, dt_off, dt_bias, a_log, Dp, cu_q, seq_slot, n_seqs, cht, heads, groups, N, dv, state, cstate,
+                 cdec, y);
   return launch_status();
 }
