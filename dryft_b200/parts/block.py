@@ -143,9 +143,21 @@ class GatedSum:
         self.keep = float(params.get("keep", 1.0))
         self.w = weights.load(prefix + params["gate"], "matrix") if params.get("gate") else None
         self.b = weights.load(prefix + params["gate_bias"], "vector") if self.w is not None and params.get("gate_bias") else None
+        self.source = None      # the part whose first product also forms the gate logits (``ride_with``)
+
+    def ride_with(self, part) -> bool:
+        """Let ``part``, which reads the same input, form ``W h`` inside its own first product (``part.absorb_rows``): one
+        launch less per sublayer.  True if it took the rows; the matrix then lives in the part's fused weight only."""
+        if self.w is None or self.source is not None or not hasattr(part, "absorb_rows") or not part.absorb_rows(self.w):
+            return False
+        self.source, self.w = part, None
+        return True
 
     def logits(self, h: torch.Tensor) -> Optional[torch.Tensor]:
-        """``W h`` in the activation type (the bias and the sigmoid belong to the kernel that forms the sum)."""
+        """``W h`` in the activation type (the bias and the sigmoid belong to the kernel that forms the sum).  When the rows
+        ride with a part's product this is a column slice of that product's output: ask AFTER the part has run."""
+        if self.source is not None:
+            return self.source.side_out
         return linear(h, self.w, self.rt) if self.w is not None else None
 
 
@@ -172,6 +184,9 @@ class PostNormBlock:
         if self.gate_mixer is None or (ffn is not None and self.gate_ffn is None):
             raise ValueError("the 'postnorm' arrangement needs a connection per sublayer (extra parts gate_mixer, gate_ffn)")
         self.extra = dict(extra)
+        self.gate_mixer.ride_with(mixer)
+        if ffn is not None:
+            self.gate_ffn.ride_with(ffn)
 
     def forward(self, res: Residual, ctx: StepContext, cache, state, owns_cache: bool = True) -> Residual:
         x = res.x
@@ -187,13 +202,14 @@ class PostNormBlock:
         if self.ffn is None:
             return Residual(x, h=h)
         conn = self.gate_ffn
-        gl = conn.logits(h)
         parts = getattr(self.ffn, "forward_parts", None)
         if parts is not None:
             y, wts, top = parts(h, ctx)
             sh = self.ffn.forward_shared(h) if hasattr(self.ffn, "forward_shared") else None
             ys, sg = sh if sh is not None else (None, None)
-            h = self.norm_ffn.sum_norm(x, y, conn.keep, gate=gl, gate_bias=conn.b, wts=wts, top=top, shared=ys, shared_gate=sg)
+            h = self.norm_ffn.sum_norm(x, y, conn.keep, gate=conn.logits(h), gate_bias=conn.b, wts=wts, top=top, shared=ys,
+                                       shared_gate=sg)
         else:
-            h = self.norm_ffn.sum_norm(x, self.ffn.forward(h, ctx), conn.keep, gate=gl, gate_bias=conn.b)
+            y = self.ffn.forward(h, ctx)
+            h = self.norm_ffn.sum_norm(x, y, conn.keep, gate=conn.logits(h), gate_bias=conn.b)
         return Residual(x, h=h)

@@ -101,6 +101,7 @@ class MoE:
             K.moe_grouped_lib()
         # the always-on expert: its first product also yields the per-token gate logit (one more row of the weight, padded)
         self.shared_inter = 0
+        self.side, self.side_out = None, None      # (first column, columns) of rows that ride with the always-on expert's product
         sh = params.get("shared")
         if sh is not None:
             if self.gated:
@@ -136,12 +137,25 @@ class MoE:
         K.moe_route(logits, self.groups, self.keep, self.top, idx, wts, renorm=self.renorm, bias=self.router_bias)
         return idx, wts
 
+    def absorb_rows(self, w: torch.Tensor) -> bool:
+        """Rows of another product of the same input join the always-on expert's first product (behind up | gate, padded);
+        their result is ``side_out`` after every ``forward_shared``."""
+        if not self.shared_inter or self.side is not None or w.dim() != 2 or w.shape[1] != self.hidden or w.dtype != self.w_shared_up.dtype:
+            return False
+        pad = (-w.shape[0]) % SHARED_PAD
+        fill = [torch.zeros((pad, self.hidden), dtype=w.dtype, device=w.device)] if pad else []
+        self.side = (self.w_shared_up.shape[0], w.shape[0])
+        self.w_shared_up = torch.cat([self.w_shared_up, w] + fill)
+        return True
+
     def forward_shared(self, h: torch.Tensor):
         """The always-on expert: ``(ys [n, hidden], gate logits [n, 1] or None)``, or None if there is none.  The caller
         multiplies ``ys`` by ``sigmoid(gate logit)`` and adds it to the routed experts' sum."""
         if not self.shared_inter:
             return None
         z = linear(h, self.w_shared_up, self.rt)
+        if self.side is not None:
+            self.side_out = z[:, self.side[0]:self.side[0] + self.side[1]]
         act = torch.empty((h.shape[0], self.shared_inter), dtype=h.dtype, device=h.device)
         K.relu2(z[:, :self.shared_inter], act)
         ys = linear(act, self.w_shared_down, self.rt)

@@ -93,6 +93,7 @@ class PooledWindowAttention:
         self.k_bias = weights.load(nm["k_bias"], "vector") if bias and self.own_kv else None
         self.v_bias = weights.load(nm["v_bias"], "vector") if bias and self.own_kv else None
         self.sink = weights.load(nm["sink"], "vector") if params.get("sink", False) else None
+        self.side, self.side_out = None, None      # (first column, columns) of rows that ride with the input product
         pos: PartSpec = params.get("position") or PartSpec("none")
         self.position = POSITIONS.get(pos.kind)(pos.params, self.qk_dim, rt)
         if getattr(self.position, "interleaved", False):
@@ -102,6 +103,17 @@ class PooledWindowAttention:
         self.use_prefill_kernel = rt.is_bf16 and K.pool_attention_prefill_supported(self.qk_dim, self.v_dim, self.group)
         if self.use_prefill_kernel:
             K.pool_attention_prefill_lib(self.qk_dim, self.v_dim, self.group)
+
+    def absorb_rows(self, w: torch.Tensor) -> bool:
+        """Rows of another product of the same input join the input product (behind q | k | v, from a column that is a
+        multiple of 8); their result is ``side_out`` after every ``forward``."""
+        if w.dtype != self.w_in.dtype or w.dim() != 2 or w.shape[1] != self.hidden or self.side is not None:
+            return False
+        pad = (-self.w_in.shape[0]) % 8
+        fill = [torch.zeros((pad, self.hidden), dtype=w.dtype, device=w.device)] if pad else []
+        self.side = (self.w_in.shape[0] + pad, w.shape[0])
+        self.w_in = torch.cat([self.w_in] + fill + [w])
+        return True
 
     def kv_need(self) -> Optional[KVNeed]:
         if self.size >= NO_WINDOW:
@@ -123,6 +135,8 @@ class PooledWindowAttention:
             raise ValueError("pooled_window_attention: a layer without key and value projections must read another run step's cache")
         n, dev = h.shape[0], h.device
         proj = linear(h, self.w_in, self.rt)
+        if self.side is not None:
+            self.side_out = proj[:, self.side[0]:self.side[0] + self.side[1]]
         q = torch.empty((n, self.n_heads, self.qk_dim), dtype=h.dtype, device=dev)
         pos = self.position
         K.pool_attn_prep(proj, self.q_bias, self.k_bias, self.v_bias, pos.inv_freq if self.rot else None,
