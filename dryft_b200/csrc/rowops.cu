@@ -31,7 +31,8 @@ __global__ void __launch_bounds__(ROW_THREADS) gated_postnorm_kernel(
   const int n = blockIdx.x;
   const float sg = ys == nullptr ? 0.f : (sgl != nullptr ? sigmoidf_(to_f32<T>(sgl[(size_t)n * sgl_ld])) : 1.f);
   float ss = 0.f;
-  for (int c = threadIdx.x; c < W; c += ROW_THREADS) {
+#pragma unroll 4
+  for (int c = threadIdx.x; c < W; c += ROW_THREADS) {   // unrolled: the loads of four columns are in flight together
     float acc;
     if (top > 0) {
       acc = 0.f;
@@ -47,6 +48,7 @@ __global__ void __launch_bounds__(ROW_THREADS) gated_postnorm_kernel(
   }
   const float tot = block_sum(ss, scratch);
   const float r = 1.f / sqrtf(tot / (float)W + eps);
+#pragma unroll 4
   for (int c = threadIdx.x; c < W; c += ROW_THREADS) {
     const float o = row[c] * r * w[c];
     x32[(size_t)n * W + c] = o;

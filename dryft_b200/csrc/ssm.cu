@@ -28,7 +28,7 @@
 namespace {
 constexpr int CONV_THREADS = 128;
 constexpr int SCAN_WARPS = 4;
-constexpr int MAX_NR = 8;      // state rows a lane holds at most: N <= 256
+constexpr int MAX_NR = 16;     // state rows a lane holds at most: N <= 512
 constexpr int COLS = 4;        // value columns of the state a warp owns
 constexpr int MAX_TAPS = 16;
 
@@ -246,7 +246,8 @@ void launch_scan(dim3 grid, cudaStream_t st, const float* xbc, int CH, const flo
   if (nr <= 1) DRYFT_SCAN(1);
   else if (nr <= 2) DRYFT_SCAN(2);
   else if (nr <= 4) DRYFT_SCAN(4);
-  else DRYFT_SCAN(8);
+  else if (nr <= 8) DRYFT_SCAN(8);
+  else DRYFT_SCAN(16);
 #undef DRYFT_SCAN
 }
 }  // namespace

@@ -1653,7 +1653,7 @@ def gated_group_norm(y, z, weight, parts: int, eps: float, out) -> None:
 
 
 # ----------------------------------------------------------------------------- selective state-space mixer
-SSM_MAX_STATE = 256    # state rows a head may have (a lane of the scan holds up to eight)
+SSM_MAX_STATE = 512    # state rows a head may have (a lane of the scan holds up to sixteen)
 SSM_MAX_TAPS = 16
 
 

@@ -69,7 +69,8 @@ CONFIGS: Dict[str, dict] = {
     "ssm": config([mamba()]),
     "ssm_sizes": config([mamba(heads=3, vdim=7, state=5, groups=1, conv=1, norm_groups=1, mlp=None),
                          mamba(heads=6, vdim=8, state=40, groups=3, conv=5, norm_groups=4, mlp="dense"),
-                         mamba(heads=2, vdim=36, state=33, groups=2, conv=2, norm_groups=3, mlp=moe(8, 1, 1, 8))],
+                         mamba(heads=2, vdim=36, state=33, groups=2, conv=2, norm_groups=3, mlp=moe(8, 1, 1, 8)),
+                         mamba(heads=2, vdim=3, state=300, groups=1, conv=4, norm_groups=1, mlp=None)],
                         width=40, vocab=77, eps=3e-4, alpha=0.8),
     "mixed": config([attention(mlp="dense"), attention(kv_from=0, mlp="moe"), mamba(), attention(heads=2, kv_heads=1, dim=32, vdim=16,
                      size=33, pool=5, rot_dims=16, mlp="moe"), mamba(heads=2, vdim=16, state=16, groups=1, conv=4, norm_groups=1, mlp=None),
