@@ -2,7 +2,9 @@
 every mixer alone and mixed, whole prompts, prompts against token-by-token decoding, prompts in portions down to two
 tokens, unequal batches against each request alone, slots and pages used again (poisoned), long decoding across window,
 block and page edges, the first tokens, the stream after every layer, greedy generation through ``Engine.generate`` /
-``generate_many`` (captured graphs and eager), the replay program and the command line as child processes."""
+``generate_many`` (captured graphs and eager), the replay program and the command line as child processes; the prompt
+attention kernel against the row-wise kernel, both against the plain function with one key that outweighs all others, and the
+state-space mixer with many-token steps cut into chunks."""
 
 import math
 
