@@ -133,7 +133,7 @@ def _mogelix(width: int, layers: int, heads: int, kv_heads: int, dim: int, windo
     """A Mogelix ``config.json``: every ``ssm_every``-th layer is a state-space mixer; of the attention layers every
     ``share_every``-th reads the keys and values of the nearest earlier attention layer that has its own.  The first layer's
     feed-forward is dense (the size of the experts a token uses plus the always-on one), the others are routed."""
-    rot = {"dims": dim, "base": 1000000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    rot = {"dims": dim, "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
     out, owner, n_att = [], None, 0
     for i in range(layers):
         mlp = {"kind": "dense", "ff": ff * (top + 1)} if i == 0 else \
