@@ -49,7 +49,7 @@ class LayerSpec:
     The ``*_prefix`` fields are the checkpoint name prefixes of the four parts
     (``model.layers.3.self_attn.``); each part appends its own local tensor names
     (``q_proj.weight``), so no part carries an architecture's naming.  A layer without a feed-forward
-    leaves ``ffn`` and ``norm_ffn`` ``None``; a layer with more parts (norms on both sides of a part, a
+    leaves ``ffn`` and ``norm_ffn`` ``None``; an arrangement whose feed-forward reads the mixer's norm leaves ``norm_ffn`` ``None``; a layer with more parts (norms on both sides of a part, a
     second feed-forward) lists them in ``extra``, and its block arrangement is handed them by name.
     """
 
@@ -72,11 +72,14 @@ class RunStep:
     ``layer`` indexes ``ModelSpec.layers`` and may occur more than once (the
     weights are then shared; every occurrence still owns a cache entry unless it
     borrows one).  ``cache_from`` is the index of an *earlier* run step whose
-    cache entry this step reads instead of owning one.
+    cache entry this step reads instead of owning one.  ``enter`` names a part of ``ModelSpec.joints`` that
+    transforms the stream right before this step, with the number of the pass it opens (a stretch of layers
+    that runs several times is entered anew every time): ``("loop", 2)``.
     """
 
     layer: int
     cache_from: Optional[int] = None
+    enter: Optional[Tuple[str, int]] = None
 
 
 @dataclass(frozen=True)
@@ -93,6 +96,9 @@ class ModelSpec:
     embedding_prefix: str = "model.embed_tokens."
     final_norm_prefix: str = "model.norm."
     head_prefix: str = "lm_head."
+    # parts between the layers (family "connection"), run where a ``RunStep.enter`` names them; such a part offers
+    # ``enter(res, x0, number, next_norm) -> Residual`` with ``x0`` the embedding's output
+    joints: Tuple[ExtraPart, ...] = ()
 
     def validate(self) -> None:
         if not self.layers:
@@ -100,7 +106,9 @@ class ModelSpec:
         if not self.schedule:
             raise ValueError("model spec has an empty run order")
         for i, layer in enumerate(self.layers):
-            if (layer.ffn is None) != (layer.norm_ffn is None):
+            if layer.ffn is None and layer.norm_ffn is not None:
+                raise ValueError(f"layer {i}: a norm for a feed-forward that is missing")
+            if layer.ffn is not None and layer.norm_ffn is None and layer.block in ("prenorm", "outnorm", "postnorm"):
                 raise ValueError(f"layer {i}: a feed-forward and its norm go together (one of them is missing)")
             names = [e.name for e in layer.extra]
             if len(set(names)) != len(names):
@@ -111,6 +119,8 @@ class ModelSpec:
         for i, st in enumerate(self.schedule):
             if not 0 <= st.layer < len(self.layers):
                 raise ValueError(f"run step {i} names layer {st.layer}, but there are {len(self.layers)} layers")
+            if st.enter is not None and st.enter[0] not in {j.name for j in self.joints}:
+                raise ValueError(f"run step {i} is entered through {st.enter[0]!r}, which is not among the model's joints")
             if st.cache_from is not None:
                 if not 0 <= st.cache_from < i:
                     raise ValueError(f"run step {i} borrows the cache of step {st.cache_from}, which does not run before it")

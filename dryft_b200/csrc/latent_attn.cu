@@ -129,7 +129,7 @@ __global__ void __launch_bounds__(WPB * 32) latent_attn_rows_kernel(
     const int* __restrict__ page_table, int max_pages, int page_size, const int* __restrict__ tok_slot,
     const int* __restrict__ tok_pos, const float* __restrict__ inv_freq, const float* __restrict__ inv_freq_lo,
     int interleaved, T* __restrict__ o_lat, float* __restrict__ part, int n_splits, int n_tokens, int H, int kv_rank, int rot,
-    float scale, int window) {
+    float scale, int window, const float* __restrict__ sink) {
   extern __shared__ __align__(16) float sm[];
   const int Dk = kv_rank + rot, Dq = (Dk + 3) & ~3, Dp = tile_row(Dk);
   float* tile = sm;                                  // [KT][Dp]
@@ -279,7 +279,13 @@ __global__ void __launch_bounds__(WPB * 32) latent_attn_rows_kernel(
       }
     } else {
       T* dst = o_lat + ((size_t)hd * n_tokens + n) * kv_rank;
-      const float inv = 1.f / l[i];
+      float li = l[i], keep = 1.f;
+      if (sink != nullptr) {   // a number in the denominator without key or value: it is not scaled and counts once
+        const float sk = sink[hd], m_all = fmaxf(m[i], sk);
+        keep = expf(m[i] - m_all);
+        li = li * keep + expf(sk - m_all);
+      }
+      const float inv = keep / li;
 #pragma unroll
       for (int r = 0; r < NR; ++r) {
         const int d = lane + 32 * r;
@@ -295,7 +301,7 @@ constexpr int MAX_SPLITS = 64;
 
 template <typename T>
 __global__ void latent_combine_kernel(const float* __restrict__ part, const int* __restrict__ tok_slot, T* __restrict__ o_lat,
-                                      int n_splits, int n_tokens, int H, int kv_rank) {
+                                      int n_splits, int n_tokens, int H, int kv_rank, const float* __restrict__ sink) {
   __shared__ float w[MAX_SPLITS];
   const int n = blockIdx.x, hd = blockIdx.y;
   if (tok_slot[n] < 0) return;
@@ -313,6 +319,7 @@ __global__ void latent_combine_kernel(const float* __restrict__ part, const int*
       m = fmaxf(m, ms[u]);
     }
     m = warp_max(m);
+    if (sink != nullptr) m = fmaxf(m, sink[hd]);
     float l = 0.f;
 #pragma unroll
     for (int u = 0; u < MAX_SPLITS / 32; ++u) {
@@ -320,6 +327,7 @@ __global__ void latent_combine_kernel(const float* __restrict__ part, const int*
       l = fmaf(ls[u], ms[u], l);
     }
     l = warp_sum(l);
+    if (sink != nullptr) l += expf(sink[hd] - m);           // the sink joins the denominator once, after the splits
 #pragma unroll
     for (int u = 0; u < MAX_SPLITS / 32; ++u)
       if (lane + 32 * u < n_splits) w[lane + 32 * u] = ms[u] / l;
@@ -469,7 +477,7 @@ template <typename T, int NR>
 int launch_rows(const float* q_lat, const void* q, int q_stride, int q_rot_off, const void* k_pages, const int* page_table,
                 int max_pages, int page_size, const int* tok_slot, const int* tok_pos, const float* inv_freq,
                 const float* inv_freq_lo, int interleaved, void* o_lat, float* part, int n_splits, int n_tokens, int H, int kv_rank,
-                int rot, float scale, int window, cudaStream_t st) {
+                int rot, float scale, int window, const float* sink, cudaStream_t st) {
   const int Dk = kv_rank + rot;
   const size_t smem = sizeof(float) * ((size_t)KT * tile_row(Dk) + (size_t)HPB * ((Dk + 3) & ~3) + (size_t)HPB * rot);
   int rc = opt_in(latent_attn_rows_kernel<T, NR>, smem);
@@ -478,10 +486,10 @@ int launch_rows(const float* q_lat, const void* q, int q_stride, int q_rot_off, 
   latent_attn_rows_kernel<T, NR><<<grid, WPB * 32, smem, st>>>(q_lat, (const T*)q, q_stride, q_rot_off, (const T*)k_pages, page_table,
                                                                max_pages, page_size, tok_slot, tok_pos, inv_freq, inv_freq_lo,
                                                                interleaved, (T*)o_lat, part, n_splits, n_tokens, H, kv_rank, rot, scale,
-                                                               window);
+                                                               window, sink);
   int e = launch_status();
   if (e || n_splits <= 1) return e;
-  latent_combine_kernel<T><<<dim3(n_tokens, H), 128, 0, st>>>(part, tok_slot, (T*)o_lat, n_splits, n_tokens, H, kv_rank);
+  latent_combine_kernel<T><<<dim3(n_tokens, H), 128, 0, st>>>(part, tok_slot, (T*)o_lat, n_splits, n_tokens, H, kv_rank, sink);
   return launch_status();
 }
 }  // namespace
@@ -511,7 +519,7 @@ DRYFT_API int dryft_latent_attn_rows(int is_bf16, const float* q_lat, const void
                                      const void* k_pages, const int* page_table, int max_pages, int page_size,
                                      const int* tok_slot, const int* tok_pos, const float* inv_freq, const float* inv_freq_lo,
                                      int interleaved, void* o_lat, float* part, int n_splits, int n_tokens, int H, int kv_rank,
-                                     int rot, float scale, int window, cudaStream_t st) {
+                                     int rot, float scale, int window, const float* sink, cudaStream_t st) {
   if (n_tokens <= 0) return 0;
   if (kv_rank <= 0 || kv_rank > 512 || rot < 0 || (rot & 1) || H <= 0 || (H + HPB - 1) / HPB > 65535) return DRYFT_ERR_UNSUPPORTED;
   if (n_splits < 1 || n_splits > MAX_SPLITS || (n_splits > 1 && !part)) return DRYFT_ERR_UNSUPPORTED;
@@ -519,10 +527,10 @@ DRYFT_API int dryft_latent_attn_rows(int is_bf16, const float* q_lat, const void
   const int nr = (kv_rank + 31) / 32;
 #define DRYFT_LATENT_ROWS(NR)                                                                                                      \
   return is_bf16 ? launch_rows<bf, NR>(q_lat, q, q_stride, q_rot_off, k_pages, page_table, max_pages, page_size, tok_slot, tok_pos,  \
-                                       inv_freq, inv_freq_lo, interleaved, o_lat, part, n_splits, n_tokens, H, kv_rank, rot, scale, window, st) \
+                                       inv_freq, inv_freq_lo, interleaved, o_lat, part, n_splits, n_tokens, H, kv_rank, rot, scale, window, sink, st) \
                  : launch_rows<float, NR>(q_lat, q, q_stride, q_rot_off, k_pages, page_table, max_pages, page_size, tok_slot,      \
                                           tok_pos, inv_freq, inv_freq_lo, interleaved, o_lat, part, n_splits, n_tokens, H, kv_rank, rot, scale, \
-                                          window, st)
+                                          window, sink, st)
   if (nr <= 1) { DRYFT_LATENT_ROWS(1); }
   if (nr <= 2) { DRYFT_LATENT_ROWS(2); }
   if (nr <= 4) { DRYFT_LATENT_ROWS(4); }

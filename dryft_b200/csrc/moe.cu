@@ -1,6 +1,6 @@
 // Mixture of experts: the router's choice and the experts evaluated assignment by assignment.
 //
-//   moe_route     scores s = softmax(logits) over all E experts (32-bit).  Expert e belongs to group e / (E / n_groups)
+//   moe_route     scores s = softmax(logits) over all E experts (32-bit), or (bit 1 of `renorm` set) s_e = sigmoid(logit_e).  Expert e belongs to group e / (E / n_groups)
 //                 (contiguous, equally sized); a group is ranked by the maximum score among its members, and selection
 //                 is restricted to the `keep` highest-ranked groups
 //                 (n_groups = keep = 1: no groups).  The `top` allowed experts with the largest scores are chosen;
@@ -14,6 +14,9 @@
 //                   mode 0:  act[a, f] = silu(Wg_e[f] . h[token]) * (Wu_e[f] . h[token])      (W_gu [E, 2F, K]: gate rows, then up rows)
 //                   mode 1:  y[a, c]   = Wd_e[c] . act[a]                                    (W_d [E, C, F])
 //                   mode 2:  act[a, f] = max(Wu_e[f] . h[token], 0)^2                         (W_u [E, F, K]: experts without a gate)
+//                   mode 3:  the assignment's weight s = in_w[a] scales the expert's INPUT, and the activation is clamped:
+//                            g = min(s * Wg_e[f] . h, limit), u = clamp(s * Wu_e[f] . h, -limit, limit),
+//                            act[a, f] = g * sigmoid(alpha * g) * (u + up_off)
 //                 32-bit accumulation in a fixed order, one rounding to T at the end.
 //   moe_combine   out[n] = sum_k wts[n, k] * y[n*top + k]   (32-bit sum, rounded once) for callers that do not fold the
 //                 weighted sum into a kernel of their own.
@@ -38,18 +41,24 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 __device__ __forceinline__ void route_one(const float* z, const float* __restrict__ bias, float* s, float* gs, int lane, int n, int E,
                                           int n_groups, int keep, int top, int renorm, int* __restrict__ idx_out,
                                           float* __restrict__ w_out) {
-  float mx = -INFINITY;
-  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e] + (bias != nullptr ? bias[e] : 0.f));
-  mx = warp_max(mx);
-  float sum = 0.f;
-  for (int e = lane; e < E; e += 32) {
-    const float p = expf(z[e] + (bias != nullptr ? bias[e] : 0.f) - mx);
-    s[e] = p;
-    sum += p;
+  const bool sigmoid_scores = renorm >= 2;      // bit 1 of `renorm`: every expert's score is the sigmoid of its own logit
+  renorm &= 1;
+  if (sigmoid_scores) {
+    for (int e = lane; e < E; e += 32) s[e] = 1.f / (1.f + expf(-(z[e] + (bias != nullptr ? bias[e] : 0.f))));
+  } else {
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e] + (bias != nullptr ? bias[e] : 0.f));
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+      const float p = expf(z[e] + (bias != nullptr ? bias[e] : 0.f) - mx);
+      s[e] = p;
+      sum += p;
+    }
+    sum = warp_sum(sum);
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) s[e] = s[e] / sum;
   }
-  sum = warp_sum(sum);
-  __syncwarp();
-  for (int e = lane; e < E; e += 32) s[e] = s[e] / sum;
   __syncwarp();
   if (n_groups > 1) {
     const int gsz = E / n_groups;
@@ -148,7 +157,7 @@ template <typename T>
 __global__ void __launch_bounds__(ROWS_THREADS) moe_rows_kernel(
     const T* __restrict__ a_in, int a_div,              // activation row of assignment a: a_in[(a / a_div) * K]
     const T* __restrict__ w, const int* __restrict__ idx, int E, int rows_per_expert, int K, int n_out, int mode,
-    T* __restrict__ out) {
+    T* __restrict__ out, const float* __restrict__ in_w, float limit, float alpha, float up_off) {
   extern __shared__ __align__(16) unsigned char smraw[];
   T* xs = reinterpret_cast<T*>(smraw);
   const int a = blockIdx.x;
@@ -163,6 +172,8 @@ __global__ void __launch_bounds__(ROWS_THREADS) moe_rows_kernel(
   constexpr int V = 16 / sizeof(T);
   const bool vec = (K % V) == 0;
   const int o_end = min(o0 + ROWS_PER_BLOCK, n_out);
+  const bool two_mats = mode == 0 || mode == 3;
+  const float in_s = mode == 3 ? in_w[a] : 1.f;
   // a warp takes two output features at a time: all their weight vectors are requested before any is used
   for (int o = o0 + 2 * warp; o < o_end; o += 2 * (ROWS_THREADS / 32)) {
     const bool two = o + 1 < o_end;
@@ -180,7 +191,7 @@ __global__ void __launch_bounds__(ROWS_THREADS) moe_rows_kernel(
 #pragma unroll
         for (int f = 0; f < 2; ++f) {
           wv[f][0] = *reinterpret_cast<const uint4*>(r[f][0] + c);
-          if (mode == 0) wv[f][1] = *reinterpret_cast<const uint4*>(r[f][1] + c);
+          if (two_mats) wv[f][1] = *reinterpret_cast<const uint4*>(r[f][1] + c);
         }
         const uint4 xv = *reinterpret_cast<const uint4*>(xs + c);
         const T* xe = reinterpret_cast<const T*>(&xv);
@@ -189,7 +200,7 @@ __global__ void __launch_bounds__(ROWS_THREADS) moe_rows_kernel(
           const T* e0 = reinterpret_cast<const T*>(&wv[f][0]);
 #pragma unroll
           for (int t = 0; t < V; ++t) d[f][0] = fmaf(to_f32<T>(e0[t]), to_f32<T>(xe[t]), d[f][0]);
-          if (mode == 0) {
+          if (two_mats) {
             const T* e1 = reinterpret_cast<const T*>(&wv[f][1]);
 #pragma unroll
             for (int t = 0; t < V; ++t) d[f][1] = fmaf(to_f32<T>(e1[t]), to_f32<T>(xe[t]), d[f][1]);
@@ -202,7 +213,7 @@ __global__ void __launch_bounds__(ROWS_THREADS) moe_rows_kernel(
 #pragma unroll
         for (int f = 0; f < 2; ++f) {
           d[f][0] = fmaf(to_f32<T>(r[f][0][c]), xv, d[f][0]);
-          if (mode == 0) d[f][1] = fmaf(to_f32<T>(r[f][1][c]), xv, d[f][1]);
+          if (two_mats) d[f][1] = fmaf(to_f32<T>(r[f][1][c]), xv, d[f][1]);
         }
       }
     }
@@ -210,6 +221,10 @@ __global__ void __launch_bounds__(ROWS_THREADS) moe_rows_kernel(
     for (int f = 0; f < 2; ++f) {
       float v = warp_sum(d[f][0]);
       if (mode == 0) v = v / (1.f + expf(-v)) * warp_sum(d[f][1]);
+      if (mode == 3) {
+        const float g = fminf(v * in_s, limit), u = fminf(fmaxf(warp_sum(d[f][1]) * in_s, -limit), limit);
+        v = g / (1.f + expf(-alpha * g)) * (u + up_off);
+      }
       if (mode == 2) { v = fmaxf(v, 0.f); v *= v; }
       if (lane == 0 && (f == 0 || two)) out[(size_t)a * n_out + o + f] = from_f32<T>(v);
     }
@@ -228,9 +243,9 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const float* __restr
 
 template <typename T>
 int rows_launch(const void* a_in, int a_div, const void* w, const int* idx, int E, int K, int n_out, int mode, void* out,
-                int n_assign, cudaStream_t st) {
+                int n_assign, const float* in_w, float limit, float alpha, float up_off, cudaStream_t st) {
   if (n_assign <= 0) return 0;
-  if (E < 1 || K < 1 || n_out < 1 || a_div < 1 || mode < 0 || mode > 2) return DRYFT_ERR_UNSUPPORTED;
+  if (E < 1 || K < 1 || n_out < 1 || a_div < 1 || mode < 0 || mode > 3 || (mode == 3 && !in_w)) return DRYFT_ERR_UNSUPPORTED;
   const size_t smem = (sizeof(T) * (size_t)K + 15) / 16 * 16;
   if (smem > 200 * 1024) return DRYFT_ERR_UNSUPPORTED;
   if (smem > 48 * 1024) {
@@ -240,8 +255,8 @@ int rows_launch(const void* a_in, int a_div, const void* w, const int* idx, int 
   const int tiles = (n_out + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
   if (tiles > 65535) return DRYFT_ERR_UNSUPPORTED;
   dim3 grid(n_assign, tiles);
-  moe_rows_kernel<T><<<grid, ROWS_THREADS, smem, st>>>((const T*)a_in, a_div, (const T*)w, idx, E, mode == 0 ? 2 * n_out : n_out, K,
-                                                      n_out, mode, (T*)out);
+  moe_rows_kernel<T><<<grid, ROWS_THREADS, smem, st>>>((const T*)a_in, a_div, (const T*)w, idx, E, (mode == 0 || mode == 3) ? 2 * n_out : n_out, K,
+                                                      n_out, mode, (T*)out, in_w, limit, alpha, up_off);
   return launch_status();
 }
 }  // namespace
@@ -258,9 +273,10 @@ DRYFT_API int dryft_moe_route(const float* logits, const float* bias, int n_toke
 }
 
 DRYFT_API int dryft_moe_rows(int is_bf16, const void* a_in, int a_div, const void* w, const int* idx, int E, int K, int n_out,
-                             int mode, void* out, int n_assign, cudaStream_t st) {
-  return is_bf16 ? rows_launch<__nv_bfloat16>(a_in, a_div, w, idx, E, K, n_out, mode, out, n_assign, st)
-                 : rows_launch<float>(a_in, a_div, w, idx, E, K, n_out, mode, out, n_assign, st);
+                             int mode, void* out, int n_assign, const float* in_w, float limit, float alpha, float up_off,
+                             cudaStream_t st) {
+  return is_bf16 ? rows_launch<__nv_bfloat16>(a_in, a_div, w, idx, E, K, n_out, mode, out, n_assign, in_w, limit, alpha, up_off, st)
+                 : rows_launch<float>(a_in, a_div, w, idx, E, K, n_out, mode, out, n_assign, in_w, limit, alpha, up_off, st);
 }
 
 DRYFT_API int dryft_moe_combine(int is_bf16, const void* y, const float* wts, int top, int width, void* out, int n, cudaStream_t st) {

@@ -87,14 +87,16 @@ __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(
 // MODE 0: A rows are h[perm[p] / top], B is W_gu[e] ([2F, K]: gate rows then up rows), out is act[p, F]
 // MODE 1: A rows are act[p],           B is W_d[e]  ([C, K]),                        out is y[perm[p], C]
 // MODE 2: A rows are h[perm[p] / top], B is W_u[e]  ([F, K]: experts without a gate), out is act[p, F] = max(., 0)^2
+// MODE 3: as MODE 0 with the assignment's weight on the expert's INPUT and a clamped activation: with s = in_w[perm[p]],
+//         g = min(s * gate, limit), u = clamp(s * up, -limit, limit), act[p, f] = g * sigmoid(alpha * g) * (u + up_off)
 // A block of 2 x 2 warps computes BM sorted rows x BN output columns (of gate AND up in mode 0), a warp BM/2 x BN/2.
 template <int MODE, int BM, int BN>
 __global__ void __launch_bounds__(128) moe_grouped_kernel(
     const bf16* __restrict__ a_in, const bf16* __restrict__ w, const int* __restrict__ offsets, const int* __restrict__ perm,
     const int* __restrict__ tile_expert, const int* __restrict__ tile_row0, const int* __restrict__ n_tiles, int top, int K,
-    int n_out, bf16* __restrict__ out) {
+    int n_out, bf16* __restrict__ out, const float* __restrict__ in_w, float limit, float alpha, float up_off) {
   constexpr int NTHREADS = 128;
-  constexpr int NMAT = MODE == 0 ? 2 : 1;       // weight matrices multiplied at once (gate and up)
+  constexpr int NMAT = (MODE == 0 || MODE == 3) ? 2 : 1;       // weight matrices multiplied at once (gate and up)
   constexpr int NB = NMAT * BN;                 // weight rows a block reads per k slice
   constexpr int WM = BM / 2, WN = BN / 2;       // a warp's rows and columns
   constexpr int MT = WM / 16, NT = WN / 8;
@@ -130,7 +132,7 @@ __global__ void __launch_bounds__(128) moe_grouped_kernel(
       const int r = i / CPR, c = i % CPR;
       int wr = n0 + (r % BN);
       const bool ok = wr < n_out && k0 + c * 8 < K;
-      if (MODE == 0 && r >= BN) wr += n_out;   // the matching up rows
+      if ((MODE == 0 || MODE == 3) && r >= BN) wr += n_out;   // the matching up rows
       cp_async16(b_st + r * LDS + c * 8, we + (ok ? (size_t)wr * K + k0 + c * 8 : 0), ok ? 16 : 0);
     }
   };
@@ -205,6 +207,17 @@ __global__ void __launch_bounds__(128) moe_grouped_kernel(
         v2 = v2 / (1.f + expf(-v2)) * acc[NMAT - 1][i][j][2];
         v3 = v3 / (1.f + expf(-v3)) * acc[NMAT - 1][i][j][3];
       }
+      if (MODE == 3) {
+        const float s0 = r0 < rows ? in_w[perm[p0 + r0]] : 0.f, s1 = r1 < rows ? in_w[perm[p0 + r1]] : 0.f;
+        const float sc[4] = {s0, s0, s1, s1};
+        float* v[4] = {&v0, &v1, &v2, &v3};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float gq = fminf(*v[q] * sc[q], limit);
+          const float uq = fminf(fmaxf(acc[NMAT - 1][i][j][q] * sc[q], -limit), limit);
+          *v[q] = gq / (1.f + expf(-alpha * gq)) * (uq + up_off);
+        }
+      }
       if (MODE == 2) {
         v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); v2 = fmaxf(v2, 0.f); v3 = fmaxf(v3, 0.f);
         v0 *= v0; v1 *= v1; v2 *= v2; v3 *= v3;
@@ -217,9 +230,10 @@ __global__ void __launch_bounds__(128) moe_grouped_kernel(
 
 template <int MODE, int BM, int BN>
 int gemm_launch(const void* a_in, const void* w, const int* offsets, const int* perm, const int* tile_expert, const int* tile_row0,
-                const int* n_tiles, int top, int K, int n_out, void* out, int max_tiles, cudaStream_t st) {
+                const int* n_tiles, int top, int K, int n_out, void* out, int max_tiles, cudaStream_t st,
+                const float* in_w = nullptr, float limit = 0.f, float alpha = 1.f, float up_off = 0.f) {
   static bool attr_set = false;   // set by the first (eager) launch, outside any stream capture
-  constexpr size_t smem = sizeof(bf16) * (size_t)LDS * STAGES * (BM + (MODE == 0 ? 2 * BN : BN));
+  constexpr size_t smem = sizeof(bf16) * (size_t)LDS * STAGES * (BM + ((MODE == 0 || MODE == 3) ? 2 * BN : BN));
   if (smem > 48 * 1024 && !attr_set) {
     cudaError_t e = cudaFuncSetAttribute(moe_grouped_kernel<MODE, BM, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -229,7 +243,7 @@ int gemm_launch(const void* a_in, const void* w, const int* offsets, const int* 
   if (n_tiles_n > 65535) return DRYFT_ERR_UNSUPPORTED;
   dim3 grid(max_tiles, n_tiles_n);
   moe_grouped_kernel<MODE, BM, BN><<<grid, 128, smem, st>>>((const bf16*)a_in, (const bf16*)w, offsets, perm, tile_expert,
-                                                          tile_row0, n_tiles, top, K, n_out, (bf16*)out);
+                                                          tile_row0, n_tiles, top, K, n_out, (bf16*)out, in_w, limit, alpha, up_off);
   return launch_status();
 }
 
@@ -257,11 +271,13 @@ DRYFT_API long long dryft_moe_grouped_work_ints(int n_assign, int E) {
 }
 
 // y[n*top, C] = experts of idx[n, top] applied to h[n, W]; act [n*top, F] is scratch (sorted order)
-// `gated`: 1 = w_gate_up is [E, 2F, W] and the activation is silu(gate) * up; 0 = it is [E, F, W] and the activation is max(., 0)^2
+// `gated`: 1 = w_gate_up is [E, 2F, W] and the activation is silu(gate) * up; 0 = it is [E, F, W] and the activation is max(., 0)^2;
+// 2 = [E, 2F, W] with the clamped activation of MODE 3 (in_w [n*top]: each assignment's weight on the expert's input)
 DRYFT_API int dryft_moe_grouped(const void* h, const void* w_gate_up, const void* w_down, const int* idx, int n_tokens, int top,
-                                int E, int W, int F, void* act, void* y, int* work, int gated, cudaStream_t st) {
+                                int E, int W, int F, void* act, void* y, int* work, int gated, const float* in_w, float limit,
+                                float alpha, float up_off, cudaStream_t st) {
   if (n_tokens <= 0) return 0;
-  if (top < 1 || E < 1 || W % 16 || F % 16 || W < 16 || F < 16) return DRYFT_ERR_UNSUPPORTED;
+  if (top < 1 || E < 1 || W % 16 || F % 16 || W < 16 || F < 16 || gated < 0 || gated > 2 || (gated == 2 && !in_w)) return DRYFT_ERR_UNSUPPORTED;
   const long long n_assign_ll = (long long)n_tokens * top;
   if (n_assign_ll > (1LL << 30) || (size_t)E * 2 * sizeof(int) > 48 * 1024) return DRYFT_ERR_UNSUPPORTED;
   const int n_assign = (int)n_assign_ll;
@@ -276,13 +292,17 @@ DRYFT_API int dryft_moe_grouped(const void* h, const void* w_gate_up, const void
   int rc = launch_status();
   if (rc) return rc;
   if (bm == 128) {
-    rc = gated ? gemm_launch<0, 128, 64>(h, w_gate_up, offsets, perm, tile_expert, tile_row0, n_tiles, top, W, F, act, max_tiles, st)
-               : gemm_launch<2, 128, 64>(h, w_gate_up, offsets, perm, tile_expert, tile_row0, n_tiles, top, W, F, act, max_tiles, st);
+    rc = gated == 2 ? gemm_launch<3, 128, 64>(h, w_gate_up, offsets, perm, tile_expert, tile_row0, n_tiles, top, W, F, act, max_tiles, st,
+                                              in_w, limit, alpha, up_off)
+         : gated    ? gemm_launch<0, 128, 64>(h, w_gate_up, offsets, perm, tile_expert, tile_row0, n_tiles, top, W, F, act, max_tiles, st)
+                    : gemm_launch<2, 128, 64>(h, w_gate_up, offsets, perm, tile_expert, tile_row0, n_tiles, top, W, F, act, max_tiles, st);
     if (rc) return rc;
     return gemm_launch<1, 128, 128>(act, w_down, offsets, perm, tile_expert, tile_row0, n_tiles, top, F, W, y, max_tiles, st);
   }
-  rc = gated ? gemm_launch<0, 64, 64>(h, w_gate_up, offsets, perm, tile_expert, tile_row0, n_tiles, top, W, F, act, max_tiles, st)
-             : gemm_launch<2, 64, 64>(h, w_gate_up, offsets, perm, tile_expert, tile_row0, n_tiles, top, W, F, act, max_tiles, st);
+  rc = gated == 2 ? gemm_launch<3, 64, 64>(h, w_gate_up, offsets, perm, tile_expert, tile_row0, n_tiles, top, W, F, act, max_tiles, st,
+                                           in_w, limit, alpha, up_off)
+       : gated    ? gemm_launch<0, 64, 64>(h, w_gate_up, offsets, perm, tile_expert, tile_row0, n_tiles, top, W, F, act, max_tiles, st)
+                  : gemm_launch<2, 64, 64>(h, w_gate_up, offsets, perm, tile_expert, tile_row0, n_tiles, top, W, F, act, max_tiles, st);
   if (rc) return rc;
   return gemm_launch<1, 64, 128>(act, w_down, offsets, perm, tile_expert, tile_row0, n_tiles, top, F, W, y, max_tiles, st);
 }

@@ -11,6 +11,10 @@
 //   pool_attn_prep    per token: q, k (+ bias) rotated over their first `rot` dims (dims i and i + rot/2 turn together by
 //                     the angle pos * inv_freq[i], evaluated in 32-bit), THEN divided by their root mean square over D
 //                     (no weight; skipped when eps < 0); v (+ bias); k and v written into the cache at the token's position.  One warp a vector.
+//   pool_attn_prep_tok  the same per token for projections that are normed as a whole: q (all H * D values at once) and k (all
+//                     G * D) are divided by their root mean square and multiplied by a weight per entry BEFORE the rotation,
+//                     and the rotation pairs either dims i and i + rot/2 or (interleaved) dims 2i and 2i + 1.  One block a
+//                     token: the two sums of squares first, then a warp a vector.
 //   pool_attn_blocks  every token that completes a block (pos % P == P - 1) averages the block's P cached keys and
 //                     values into the pooled pages.  One block per (token, kv head); all others return at once.
 //   pool_attn_rows    one block per (token, kv head, split): the REP query heads of the kv head over the visible pooled
@@ -112,6 +116,87 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) pool_attn_prep_kernel(
   for (int r = 0; r < DR; ++r) {
     const int c = lane + 32 * r;
     if (c < D) dst[c] = from_f32<T>(o[r] * rinv);
+  }
+}
+
+// One block per token.  q_w [H * D] / k_w [G * D]: the weights of a norm over the whole projection (nullptr: no such norm).
+template <typename T>
+__global__ void __launch_bounds__(PREP_WARPS * 32) pool_attn_prep_tok_kernel(
+    const T* __restrict__ proj, int ld, const float* __restrict__ q_w, const float* __restrict__ k_w, float norm_eps,
+    const float* __restrict__ inv_freq, const float* __restrict__ inv_freq_lo, int rot, int interleaved, const int* __restrict__ tok_slot,
+    const int* __restrict__ tok_pos, T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
+    const int* __restrict__ page_table, int max_pages, int page_size, int H, int G, float eps, int write_kv) {
+  __shared__ float sm[PREP_WARPS][D];
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  const int slot = tok_slot[t];
+  if (slot < 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pos = tok_pos[t];
+  const T* row = proj + (size_t)t * ld;
+  float rq = 1.f, rk = 1.f;
+  if (q_w != nullptr) {
+    float a = 0.f;
+    for (int c = threadIdx.x; c < H * D; c += PREP_WARPS * 32) { const float v = to_f32<T>(row[c]); a = fmaf(v, v, a); }
+    rq = 1.f / sqrtf(block_sum(a, scratch) / (float)(H * D) + norm_eps);
+  }
+  if (k_w != nullptr && write_kv) {
+    float a = 0.f;
+    for (int c = threadIdx.x; c < G * D; c += PREP_WARPS * 32) { const float v = to_f32<T>(row[(size_t)H * D + c]); a = fmaf(v, v, a); }
+    rk = 1.f / sqrtf(block_sum(a, scratch) / (float)(G * D) + norm_eps);
+  }
+  size_t cache_row0 = 0;
+  if (write_kv) cache_row0 = (size_t)page_table[(size_t)slot * max_pages + pos / page_size];
+  const int per_tok = H + (write_kv ? 2 * G : 0);
+  const int half = rot / 2;
+  const float fpos = (float)pos;
+  float* s = sm[warp];
+  for (int vec = warp; vec < per_tok; vec += PREP_WARPS) {
+    if (vec >= H + G) {     // a value vector: into the cache as it is
+      const int g = vec - H - G;
+      const size_t cr = (cache_row0 * G + g) * page_size + pos % page_size;
+      const T* src = row + (size_t)H * D + (size_t)G * D + (size_t)g * DV;
+      for (int c = lane; c < DV; c += 32) v_pages[cr * DV + c] = src[c];
+      continue;
+    }
+    const bool is_q = vec < H;
+    const int hd = is_q ? vec : vec - H;
+    const T* src = row + (is_q ? (size_t)hd * D : (size_t)H * D + (size_t)hd * D);
+    const float* w = is_q ? q_w : k_w;
+    const float r = is_q ? rq : rk;
+    __syncwarp();
+    for (int c = lane; c < D; c += 32) s[c] = w != nullptr ? to_f32<T>(src[c]) * r * w[hd * D + c] : to_f32<T>(src[c]);
+    __syncwarp();
+    float o[DR];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < DR; ++k) {
+      const int c = lane + 32 * k;
+      float v = 0.f;
+      if (c < D) {
+        if (c < rot) {
+          // the entry this one turns with, the pair's frequency, and which of the two it is
+          const int i = interleaved ? (c >> 1) : (c < half ? c : c - half);
+          const bool first = interleaved ? !(c & 1) : c < half;
+          const int other = interleaved ? (c ^ 1) : (first ? c + half : c - half);
+          float sn, cs;
+          sincos_split(fpos, inv_freq[i], inv_freq_lo != nullptr ? inv_freq_lo[i] : 0.f, &sn, &cs);
+          v = first ? s[c] * cs - s[other] * sn : s[c] * cs + s[other] * sn;
+        } else {
+          v = s[c];
+        }
+      }
+      o[k] = v;
+      ss = fmaf(v, v, ss);
+    }
+    float rinv = 1.f;
+    if (eps >= 0.f) rinv = 1.f / sqrtf(warp_sum(ss) / (float)D + eps);    // eps < 0: no unit norm
+    T* dst = is_q ? q_out + ((size_t)t * H + hd) * D : k_pages + ((cache_row0 * G + hd) * page_size + pos % page_size) * D;
+#pragma unroll
+    for (int k = 0; k < DR; ++k) {
+      const int c = lane + 32 * k;
+      if (c < D) dst[c] = from_f32<T>(o[k] * rinv);
+    }
   }
 }
 
@@ -361,6 +446,25 @@ DRYFT_API int dryft_pool_attn_prep(int is_bf16, const void* proj, int ld, const 
                                               max_pages, page_size, n, H, G, eps, write_kv, st)
                  : prep_launch<float>(proj, ld, qb, kb, vb, inv_freq, inv_freq_lo, rot, tok_slot, tok_pos, q_out, k_pages, v_pages, page_table,
                                       max_pages, page_size, n, H, G, eps, write_kv, st);
+}
+
+DRYFT_API int dryft_pool_attn_prep_tok(int is_bf16, const void* proj, int ld, const float* q_w, const float* k_w, float norm_eps,
+                                       const float* inv_freq, const float* inv_freq_lo, int rot, int interleaved, const int* tok_slot,
+                                       const int* tok_pos, void* q_out, void* k_pages, void* v_pages, const int* page_table, int max_pages,
+                                       int page_size, int n, int H, int G, float eps, int write_kv, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (H != G * REP || rot < 0 || rot % 2 || rot > D || (rot > 0 && inv_freq == nullptr) || (write_kv && page_size < 1))
+    return DRYFT_ERR_UNSUPPORTED;
+  typedef __nv_bfloat16 bf;
+  if (is_bf16)
+    pool_attn_prep_tok_kernel<bf><<<n, PREP_WARPS * 32, 0, st>>>((const bf*)proj, ld, q_w, k_w, norm_eps, inv_freq, inv_freq_lo, rot, interleaved,
+                                                                 tok_slot, tok_pos, (bf*)q_out, (bf*)k_pages, (bf*)v_pages, page_table, max_pages,
+                                                                 page_size, H, G, eps, write_kv);
+  else
+    pool_attn_prep_tok_kernel<float><<<n, PREP_WARPS * 32, 0, st>>>((const float*)proj, ld, q_w, k_w, norm_eps, inv_freq, inv_freq_lo, rot,
+                                                                    interleaved, tok_slot, tok_pos, (float*)q_out, (float*)k_pages,
+                                                                    (float*)v_pages, page_table, max_pages, page_size, H, G, eps, write_kv);
+  return launch_status();
 }
 
 DRYFT_API int dryft_pool_attn_blocks(int is_bf16, const void* k_pages, const void* v_pages, const int* page_table, int max_pages,

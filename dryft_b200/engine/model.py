@@ -32,7 +32,8 @@ class DecoderModel:
             mixer = MIXERS.get(layer.mixer.kind)(layer.mixer.params, layer.mixer_prefix, weights, rt)
             norm_ffn = ffn = None
             if layer.ffn is not None:
-                norm_ffn = NORMS.get(layer.norm_ffn.kind)(layer.norm_ffn.params, layer.norm_ffn_prefix, weights, rt)
+                if layer.norm_ffn is not None:
+                    norm_ffn = NORMS.get(layer.norm_ffn.kind)(layer.norm_ffn.params, layer.norm_ffn_prefix, weights, rt)
                 ffn = FFNS.get(layer.ffn.kind)(layer.ffn.params, layer.ffn_prefix, weights, rt)
             extra = {e.name: FAMILIES[e.family].get(e.spec.kind)(e.spec.params, e.prefix, weights, rt) for e in layer.extra}
             make = BLOCKS.get(layer.block)
@@ -41,6 +42,9 @@ class DecoderModel:
         self.layer_tap = None
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm.params, spec.final_norm_prefix, weights, rt)
         self.head = HEADS.get(spec.head.kind)(spec.head.params, spec.head_prefix, weights, rt, embedding=self.embedding)
+        # parts between the layers: what a run step is entered through
+        self.joints = {j.name: FAMILIES[j.family].get(j.spec.kind)(j.spec.params, j.prefix, weights, rt) for j in spec.joints}
+        self.keeps_x0 = any(st.enter is not None for st in spec.schedule)
 
     # what each run step asks of the cache
     def cache_needs(self) -> Tuple[List[Tuple[Optional[KVNeed], Optional[StateNeed]]], List[Optional[int]]]:
@@ -68,6 +72,8 @@ class DecoderModel:
                         seen.add(key)
                         total += v.numel() * v.element_size()
         visit(self.embedding); visit(self.final_norm); visit(self.head)
+        for j in self.joints.values():
+            visit(j)
         for b in self.blocks:
             for part in (b.norm_mixer, b.mixer, b.norm_ffn, b.ffn, *getattr(b, "extra", {}).values()):
                 if part is not None:
@@ -88,11 +94,18 @@ class DecoderModel:
         if not isinstance(res, Residual):
             res = Residual(res)
         sched = self.spec.schedule
+        x0 = res.x.clone() if self.keeps_x0 else None    # the embedding's output, for the joints that mix it back in
         for i, st in enumerate(sched):
             block = self.blocks[st.layer]
+            if st.enter is not None:
+                res = self.joints[st.enter[0]].enter(res, x0, st.enter[1], getattr(block, "norm_mixer", None))
             if getattr(block, "takes_next_norm", False):
-                # the norm that reads the stream next: the following run step's first norm, or the final norm
-                nxt = getattr(self.blocks[sched[i + 1].layer], "norm_mixer", None) if i + 1 < len(sched) else self.final_norm
+                # the norm that reads the stream next: the following run step's first norm, or the final norm -- unless a
+                # joint transforms the stream in between
+                if i + 1 < len(sched):
+                    nxt = None if sched[i + 1].enter is not None else getattr(self.blocks[sched[i + 1].layer], "norm_mixer", None)
+                else:
+                    nxt = self.final_norm
                 res = block.forward(res, ctx, cache.entry(i), cache.state(i), owns_cache=st.cache_from is None, next_norm=nxt)
             else:
                 res = block.forward(res, ctx, cache.entry(i), cache.state(i), owns_cache=st.cache_from is None)
@@ -106,7 +119,10 @@ class DecoderModel:
                 and self.head.can_fuse(res.x.shape[0], self.final_norm)):
             xw = res.xw if res.xw_norm is self.final_norm else None
             return self.head.forward_normed(res.x, res.ss, res.ss_parts, self.final_norm, **({"xw": xw} if xw is not None else {}))
-        if res.delta is None:
+        if res.delta is None and res.hn is not None and res.hn_norm is self.final_norm:
+            # the kernel that formed the stream left it normed already: only the wanted rows go on
+            h = res.hn if all_rows else res.hn.index_select(0, want_rows[:n_want].long())
+        elif res.delta is None:
             h = self.final_norm.forward(res.x, rows=want_rows, n_rows=n_want)
         else:
             h = self.final_norm.add_forward(res.x, res.delta, rows=want_rows, n_rows=n_want)

@@ -69,7 +69,7 @@ def core() -> ctypes.CDLL:
             lib.dryft_stream_norm_rows.argtypes = [_i, _i, _p, _p, _p, _f, _f, _p, _i, _i, _p]
             lib.dryft_kv_maps_store.argtypes = [_i, _p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p]
             lib.dryft_moe_route.argtypes = [_p, _p, _i, _i, _i, _i, _i, _i, _p, _p, _p]
-            lib.dryft_moe_rows.argtypes = [_i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _i, _p]
+            lib.dryft_moe_rows.argtypes = [_i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _i, _p, _f, _f, _f, _p]
             lib.dryft_moe_combine.argtypes = [_i, _p, _p, _i, _i, _p, _i, _p]
             lib.dryft_moe_route_rows.argtypes = [_i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p]
             for name in ("dryft_step_meta", "dryft_step_advance", "dryft_tokens_from_state", "dryft_embed",
@@ -760,16 +760,23 @@ def diff_attn_rows(q, k_pages, v_pages, page_table, tok_slot, tok_pos, out, scal
 
 
 # ----------------------------------------------------------------------------- mixture of experts
-def moe_route(logits, n_groups: int, keep: int, top: int, idx_out, w_out, renorm: bool = False, bias=None) -> None:
+def _route_flags(renorm: bool, score: str) -> int:
+    if score not in ("softmax", "sigmoid"):
+        raise KernelError(f"moe_route: scores are 'softmax' or 'sigmoid', got {score!r}")
+    return int(bool(renorm)) | (2 if score == "sigmoid" else 0)
+
+
+def moe_route(logits, n_groups: int, keep: int, top: int, idx_out, w_out, renorm: bool = False, bias=None, score: str = "softmax") -> None:
     """The router's choice per token from 32-bit ``logits [n, experts]`` (plus ``bias [experts]``, if given): ``idx_out [n, top]``
-    int32, ``w_out [n, top]`` float32.  ``renorm``: the chosen scores divided by their sum (a softmax over the chosen logits)."""
+    int32, ``w_out [n, top]`` float32.  ``renorm``: the chosen scores divided by their sum (a softmax over the chosen logits).
+    ``score="sigmoid"``: an expert's score is the sigmoid of its own logit instead of the softmax over all of them."""
     n, e = logits.shape
     _need(logits, "router logits", torch.float32)
     if bias is not None:
         _need(bias, "router bias", torch.float32, (e,))
     _need(idx_out, "idx_out", torch.int32, (n, top))
     _need(w_out, "w_out", torch.float32, (n, top))
-    _ok(core().dryft_moe_route(_ptr(logits), _ptr(bias), n, e, int(n_groups), int(keep), int(top), int(renorm), _ptr(idx_out), _ptr(w_out),
+    _ok(core().dryft_moe_route(_ptr(logits), _ptr(bias), n, e, int(n_groups), int(keep), int(top), _route_flags(renorm, score), _ptr(idx_out), _ptr(w_out),
                                _stream()), f"moe_route ({e} experts, {n_groups} groups, keep {keep}, top {top})")
 
 
@@ -778,7 +785,8 @@ def moe_route_rows_supported(hidden: int, experts: int, groups: int, itemsize: i
     return 4 * (2 * experts + groups) + (itemsize * hidden + 15) // 16 * 16 <= 48 * 1024
 
 
-def moe_route_rows(h, w_router, n_groups: int, keep: int, top: int, idx_out, w_out, renorm: bool = False, bias=None) -> None:
+def moe_route_rows(h, w_router, n_groups: int, keep: int, top: int, idx_out, w_out, renorm: bool = False, bias=None,
+                   score: str = "softmax") -> None:
     """``moe_route`` of ``logits = h @ w_router.T`` (32-bit sums) in one launch, for few tokens: one block per token."""
     n, k = h.shape
     e = w_router.shape[0]
@@ -788,12 +796,14 @@ def moe_route_rows(h, w_router, n_groups: int, keep: int, top: int, idx_out, w_o
     _need(w_out, "w_out", torch.float32, (n, top))
     if bias is not None:
         _need(bias, "router bias", torch.float32, (e,))
-    _ok(core().dryft_moe_route_rows(_act(h, "h"), _ptr(h), _ptr(w_router), _ptr(bias), n, k, e, int(n_groups), int(keep), int(top), int(renorm),
+    _ok(core().dryft_moe_route_rows(_act(h, "h"), _ptr(h), _ptr(w_router), _ptr(bias), n, k, e, int(n_groups), int(keep), int(top), _route_flags(renorm, score),
                                     _ptr(idx_out), _ptr(w_out), _stream()), f"moe_route_rows ({e} experts over {k})")
 
 
-def moe_rows(a, w, idx, out, mode: str) -> None:
+def moe_rows(a, w, idx, out, mode: str, in_w=None, limit: Optional[float] = None, alpha: float = 1.0, up_offset: float = 0.0) -> None:
     """Experts evaluated assignment by assignment.  ``idx [n, top]`` int32 names each assignment's expert.
+    ``mode="gate_up_clamp"``: as ``gate_up`` with the assignment's weight ``s = in_w[n, k]`` on the expert's input and a clamped
+    activation: ``g = min(s * gate, limit)``, ``u = clamp(s * up, -limit, limit)``, ``out = g * sigmoid(alpha * g) * (u + up_offset)``;
     ``mode="gate_up"``: ``a [n, K]`` token rows, ``w [E, 2F, K]``, ``out [n*top, F] = silu(gate) * up``;
     ``mode="down"``: ``a [n*top, F]``, ``w [E, C, F]``, ``out [n*top, C]``;
     ``mode="up_relu2"`` (experts without a gate): ``a [n, K]``, ``w [E, F, K]``, ``out [n*top, F] = max(up, 0)^2``."""
@@ -803,9 +813,11 @@ def moe_rows(a, w, idx, out, mode: str) -> None:
     _need(a, "a")
     _need(w, "w", a.dtype)
     e, r, k = w.shape
-    if mode == "gate_up":
+    if mode in ("gate_up", "gate_up_clamp"):
         top = idx.shape[1]
-        n_out, code, a_div = r // 2, 0, top
+        n_out, code, a_div = r // 2, (0 if mode == "gate_up" else 3), top
+        if mode == "gate_up_clamp":
+            _need(in_w, "in_w", torch.float32, tuple(idx.shape))
         if a.shape != (idx.shape[0], k) or r % 2:
             raise KernelError(f"moe_rows: activations {tuple(a.shape)} against weights {tuple(w.shape)}")
     elif mode == "up_relu2":
@@ -819,7 +831,9 @@ def moe_rows(a, w, idx, out, mode: str) -> None:
     else:
         raise KernelError(f"moe_rows: unknown mode {mode!r}")
     _need(out, "out", a.dtype, (n_assign, n_out))
-    _ok(core().dryft_moe_rows(is_bf16, _ptr(a), a_div, _ptr(w), _ptr(idx), e, k, n_out, code, _ptr(out), n_assign, _stream()),
+    _ok(core().dryft_moe_rows(is_bf16, _ptr(a), a_div, _ptr(w), _ptr(idx), e, k, n_out, code, _ptr(out), n_assign,
+                              _ptr(in_w if code == 3 else None), float("inf") if limit is None else float(limit), float(alpha),
+                              float(up_offset), _stream()),
         f"moe_rows ({mode}, K={k}, out={n_out})")
 
 
@@ -908,7 +922,7 @@ def moe_grouped_lib() -> ctypes.CDLL:
                 if os.environ.get(var):
                     defs[name] = int(os.environ[var])
             lib = _load(build.build_library("moe_grouped", ("moe_grouped.cu",), defs))
-            lib.dryft_moe_grouped.argtypes = [_p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p, _p, _i, _p]
+            lib.dryft_moe_grouped.argtypes = [_p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p, _p, _i, _p, _f, _f, _f, _p]
             lib.dryft_moe_grouped.restype = _i
             lib.dryft_moe_grouped_work_ints.argtypes = [_i, _i]
             lib.dryft_moe_grouped_work_ints.restype = _ll
@@ -916,10 +930,13 @@ def moe_grouped_lib() -> ctypes.CDLL:
         return _moe_grouped
 
 
-def moe_grouped(h, w_gate_up, w_down, idx, y, gated: bool = True) -> None:
+def moe_grouped(h, w_gate_up, w_down, idx, y, gated: bool = True, in_w=None, limit: Optional[float] = None, alpha: float = 1.0,
+                up_offset: float = 0.0) -> None:
     """``y[n*top + k] = expert idx[n, k] applied to h[n]`` (bfloat16) with the assignments sorted by expert on the device and
     both expert products as grouped tensor-core products (``csrc/moe_grouped.cu``: three launches, no host round trip).
-    ``gated=False``: ``w_gate_up`` is ``[E, F, W]`` (no gate rows) and the activation is ``max(., 0)^2``."""
+    ``gated=False``: ``w_gate_up`` is ``[E, F, W]`` (no gate rows) and the activation is ``max(., 0)^2``.  With ``in_w [n, top]``
+    (float32) each assignment's weight scales its expert's input and the activation is the clamped one of ``moe_rows``'s
+    ``gate_up_clamp`` mode."""
     n, width = h.shape
     top = idx.shape[1]
     e, two_f, _ = w_gate_up.shape
@@ -934,8 +951,13 @@ def moe_grouped(h, w_gate_up, w_down, idx, y, gated: bool = True) -> None:
     lib = moe_grouped_lib()
     work = torch.empty(int(lib.dryft_moe_grouped_work_ints(n * top, e)), dtype=torch.int32, device=h.device)
     act = torch.empty((n * top, f), dtype=torch.bfloat16, device=h.device)
+    if in_w is not None:
+        if not gated:
+            raise KernelError("moe_grouped: weights on the experts' input go with gated experts")
+        _need(in_w, "in_w", torch.float32, (n, top))
     _ok(lib.dryft_moe_grouped(_ptr(h), _ptr(w_gate_up), _ptr(w_down), _ptr(idx), n, top, e, width, f, _ptr(act), _ptr(y), _ptr(work),
-                              int(gated), _stream()), f"moe_grouped ({e} experts, {width} x {f})", n_kernels=3)
+                              2 if in_w is not None else int(gated), _ptr(in_w), float("inf") if limit is None else float(limit),
+                              float(alpha), float(up_offset), _stream()), f"moe_grouped ({e} experts, {width} x {f})", n_kernels=3)
 
 
 # ----------------------------------------------------------------------------- matrix products
@@ -1246,7 +1268,7 @@ def latent_attn_lib() -> ctypes.CDLL:
         "dryft_head_gate_rows": [_i, _p, _i, _p, _i, _p, _i, _i, _i, _p],
         "dryft_latent_fold_q": [_i, _p, _i, _p, _p, _i, _i, _i, _i, _p],
         "dryft_latent_unfold_o": [_i, _p, _p, _p, _i, _p, _i, _i, _i, _i, _p],
-        "dryft_latent_attn_rows": [_i, _p, _p, _i, _i, _p, _p, _i, _i, _p, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _f, _i, _p],
+        "dryft_latent_attn_rows": [_i, _p, _p, _i, _i, _p, _p, _i, _i, _p, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _f, _i, _p, _p],
         "dryft_head_gate": [_i, _p, _p, _i, _p, _i, _i, _i, _p],
     })
 
@@ -1454,11 +1476,14 @@ def latent_prep(proj, dq_off: int, q_rank: int, w_q, dkv_off: int, kv_rank: int,
 
 
 def latent_attn_rows(q_lat, q, q_rot_off: int, k_pages, page_table, tok_slot, tok_pos, inv_freq, interleaved: bool, o_lat,
-                     kv_rank: int, rot: int, scale: float, window: Optional[int], inv_freq_lo=None, n_splits: int = 1) -> None:
+                     kv_rank: int, rot: int, scale: float, window: Optional[int], inv_freq_lo=None, n_splits: int = 1, sink=None) -> None:
     """``o_lat [H, n, kv_rank]``: softmax attention of ``q_lat [H, n, kv_rank]`` (float32, the key matrices folded in) and the
     rotated part of ``q [n, H, q_stride]`` (at ``q_rot_off``, rotated here) over the cached rows ``[c | k_rot]``.
-    ``n_splits``: blocks that share each token's visible keys (whole tiles of 32 keys each)."""
+    ``n_splits``: blocks that share each token's visible keys (whole tiles of 32 keys each).  ``sink [H]`` (float32): the
+    denominator of head ``h`` also holds ``exp(sink[h])``, which has no key and no value and is not scaled."""
     n_heads, n, _ = q_lat.shape
+    if sink is not None:
+        _need(sink, "sink", torch.float32, (n_heads,))
     _need(q_lat, "q_lat", torch.float32, (n_heads, n, kv_rank))
     _need(q, "q", k_pages.dtype, (n, n_heads, None))
     if q_rot_off + rot > q.shape[2]:
@@ -1475,7 +1500,7 @@ def latent_attn_rows(q_lat, q, q_rot_off: int, k_pages, page_table, tok_slot, to
     _ok(latent_attn_lib().dryft_latent_attn_rows(_act(k_pages, "k_pages"), _ptr(q_lat), _ptr(q), q.shape[2], int(q_rot_off), _ptr(k_pages),
                                                  _ptr(page_table), page_table.shape[1], k_pages.shape[2], _ptr(tok_slot), _ptr(tok_pos),
                                                  _ptr(inv_freq), _ptr(_freq_lo(inv_freq_lo, rot)), int(interleaved), _ptr(o_lat), _ptr(part), int(n_splits),
-                                                 n, n_heads, kv_rank, rot, float(scale), int(window or 0), _stream()),
+                                                 n, n_heads, kv_rank, rot, float(scale), int(window or 0), _ptr(sink), _stream()),
         f"latent_attn_rows (rank {kv_rank}, rotated {rot})", n_kernels=2 if n_splits > 1 else 1)
 
 
@@ -1740,7 +1765,9 @@ def pool_attention_lib(qk_dim: int, v_dim: int, group: int) -> ctypes.CDLL:
             lib.dryft_pool_attn_blocks.argtypes = [_i, _p, _p, _p, _i, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _p]
             lib.dryft_pool_attn_rows.argtypes = [_i, _p, _p, _p, _p, _i, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _f,
                                                  _i, _i, _p]
-            for fn in ("dryft_pool_attn_prep", "dryft_pool_attn_blocks", "dryft_pool_attn_rows"):
+            lib.dryft_pool_attn_prep_tok.argtypes = [_i, _p, _i, _p, _p, _f, _p, _p, _i, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i,
+                                                     _f, _i, _p]
+            for fn in ("dryft_pool_attn_prep", "dryft_pool_attn_prep_tok", "dryft_pool_attn_blocks", "dryft_pool_attn_rows"):
                 getattr(lib, fn).restype = _i
             if (lib.dryft_pool_attn_qk_dim(), lib.dryft_pool_attn_v_dim(), lib.dryft_pool_attn_group()) != (qk_dim, v_dim, group):
                 raise KernelError(f"{path} was compiled for other sizes")
@@ -1832,6 +1859,36 @@ def pool_attn_prep(proj, q_bias, k_bias, v_bias, inv_freq, inv_freq_lo, rot: int
                                  int(write_kv), _stream()), f"pool_attn_prep ({n_heads}/{n_kv} heads of {d})")
 
 
+def pool_attn_prep_tok(proj, q_norm_w, k_norm_w, norm_eps: float, inv_freq, inv_freq_lo, rot: int, interleaved: bool, tok_slot, tok_pos,
+                       q_out, k_pages, v_pages, page_table, n_heads: int, n_kv: int, eps: float, write_kv: bool) -> None:
+    """``pool_attn_prep`` for projections normed as a whole: per token of ``proj [n, H*D (+ G*D + G*DV)]`` all of q (and all of k)
+    is divided by its root mean square (``norm_eps`` inside the root) and multiplied by ``q_norm_w [H*D]`` (``k_norm_w [G*D]``)
+    BEFORE the rotation of each head's first ``rot`` dims (``interleaved``: dims ``2i`` and ``2i + 1`` turn together, else
+    ``i`` and ``i + rot/2``); then the optional unit norm per head (``eps >= 0``); k and v into the cache pages."""
+    n, ld = proj.shape
+    d, dv = q_out.shape[2], v_pages.shape[-1]
+    _need(proj, "proj")
+    _need(q_out, "q_out", proj.dtype, (n, n_heads, d))
+    _need(k_pages, "k_pages", proj.dtype, (None, n_kv, None, d))
+    _need(v_pages, "v_pages", proj.dtype, (None, n_kv, k_pages.shape[2], dv))
+    _need(page_table, "page_table", torch.int32)
+    if ld < n_heads * d + (n_kv * (d + dv) if write_kv else 0):
+        raise KernelError(f"pool_attn_prep_tok: a row of {ld} values is too short for {n_heads} + {n_kv} heads")
+    if q_norm_w is not None:
+        _need(q_norm_w, "q_norm_w", torch.float32, (n_heads * d,))
+    if k_norm_w is not None:
+        _need(k_norm_w, "k_norm_w", torch.float32, (n_kv * d,))
+    if rot:
+        _need(inv_freq, "inv_freq", torch.float32, (rot // 2,))
+        if inv_freq_lo is not None:
+            _need(inv_freq_lo, "inv_freq_lo", torch.float32, (rot // 2,))
+    lib = pool_attention_lib(d, dv, n_heads // n_kv)
+    _ok(lib.dryft_pool_attn_prep_tok(_act(proj, "proj"), _ptr(proj), ld, _ptr(q_norm_w), _ptr(k_norm_w), float(norm_eps), _ptr(inv_freq),
+                                     _ptr(inv_freq_lo), int(rot), int(interleaved), _ptr(tok_slot), _ptr(tok_pos), _ptr(q_out),
+                                     _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.shape[1], k_pages.shape[2], n, n_heads,
+                                     n_kv, float(eps), int(write_kv), _stream()), f"pool_attn_prep_tok ({n_heads}/{n_kv} heads of {d})")
+
+
 def pool_attn_blocks(k_pages, v_pages, page_table, pk_pages, pv_pages, pool_table, tok_slot, tok_pos, n: int, pool: int,
                      group: int) -> None:
     """Every token of the step that completes a block of ``pool`` positions leaves the means of the block's cached keys and
@@ -1878,3 +1935,115 @@ def pool_attn_rows(q, k_pages, v_pages, page_table, pooled, sink, tok_slot, tok_
                                  _ptr(tok_pos), _ptr(out), _ptr(part_o), _ptr(part_ml), n, n_kv, int(n_splits), float(scale), int(size),
                                  int(pool), _stream()), f"pool_attn_rows (window {size}, blocks of {pool})",
         n_kernels=2 if n_splits > 1 else 1)
+
+
+# ----------------------------------------------------------------------------- a 32-bit stream that takes several results at once
+def stream_par_lib() -> ctypes.CDLL:
+    return _single_lib("stream_par", {
+        "dryft_stream_sum": [_i, _p, _p, _p, _f, _p, _f, _p, _f, _p, _i, _f, _p, _p, _f, _p, _i, _i, _p],
+        "dryft_pack_pair": [_i, _p, _p, _p, _i, _i, _p],
+        "dryft_softcap": [_p, _ll, _f, _p],
+    })
+
+
+def stream_sum(x32, terms=(), *, rows=None, top: int = 0, rows_scale: float = 1.0, vec=None, src=None, norm_w=None, eps: float = 0.0,
+               h=None) -> None:
+    """``x32[n] (or src[n]) + sum_i scale_i * y_i[n] + rows_scale * sum_k rows[n * top + k] + vec -> x32[n]`` in 32-bit, for up
+    to three ``terms`` ``(y_i, scale_i)`` of the activation type ``[n, width]``, ``rows [n * top, width]`` (a routed
+    feed-forward's results, summed in the order of the choices) and a 32-bit vector ``vec [width]``; with ``norm_w`` also
+    ``h[n] = T(x32[n] / sqrt(mean(x32[n]^2) + eps) * norm_w)``, the next layer's normed input."""
+    n, width = x32.shape
+    _need(x32, "x32", torch.float32)
+    terms = [(y, float(sc)) for y, sc in terms if y is not None]
+    if len(terms) > 3:
+        raise KernelError("stream_sum: at most three terms beside the routed rows")
+    act = None
+    for y, _ in terms:
+        _need(y, "term", act, (n, width))
+        act = y.dtype
+    if rows is not None:
+        if top < 1:
+            raise KernelError("stream_sum: routed rows need their count per token")
+        _need(rows, "rows", act, (n * top, width))
+        act = rows.dtype
+    if h is not None:
+        _need(h, "h", act, (n, width))
+        act = h.dtype
+    if src is not None:
+        _need(src, "src", torch.float32, (n, width))
+    if vec is not None:
+        _need(vec, "vec", torch.float32, (width,))
+    if norm_w is not None:
+        _need(norm_w, "norm_w", torch.float32, (width,))
+        if h is None:
+            raise KernelError("stream_sum: a norm needs the tensor its result goes to")
+    if act is None:
+        act = torch.float32
+    if act not in (torch.float32, torch.bfloat16):
+        raise KernelError(f"stream_sum: terms are float32 or bfloat16, got {act}")
+    terms += [(None, 0.0)] * (3 - len(terms))
+    _ok(stream_par_lib().dryft_stream_sum(int(act == torch.bfloat16), _ptr(x32), _ptr(src), _ptr(terms[0][0]), terms[0][1],
+                                          _ptr(terms[1][0]), terms[1][1], _ptr(terms[2][0]), terms[2][1], _ptr(rows), int(top),
+                                          float(rows_scale), _ptr(vec), _ptr(norm_w), float(eps), _ptr(h if norm_w is not None else None),
+                                          n, width, _stream()), "stream_sum")
+
+
+def pack_pair(a32, b32, out) -> None:
+    """``out[n] = T([a32[n] | b32[n]])``: two 32-bit rows side by side as one operand row."""
+    n, width = a32.shape
+    _need(a32, "a32", torch.float32)
+    _need(b32, "b32", torch.float32, (n, width))
+    _need(out, "out", None, (n, 2 * width))
+    _ok(stream_par_lib().dryft_pack_pair(_act(out, "out"), _ptr(a32), _ptr(b32), _ptr(out), n, width, _stream()), "pack_pair")
+
+
+def softcap(logits, cap: float) -> None:
+    """``logits <- cap * tanh(logits / cap)`` in place (float32)."""
+    _need(logits, "logits", torch.float32)
+    _ok(stream_par_lib().dryft_softcap(_ptr(logits), logits.numel(), float(cap), _stream()), "softcap")
+
+
+# ----------------------------------------------------------------------------- selective scan (a decay per channel and state)
+SELSCAN_MAX_STATE = 512
+SELSCAN_CHUNK_TOKENS = 128
+
+
+def selscan_lib() -> ctypes.CDLL:
+    return _single_lib("selscan", {
+        "dryft_selscan": [_i, _p, _p, _i, _i, _i, _p, _p, _p, _p, _p, _i, _i, _p, _p, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p],
+    })
+
+
+def selscan(xc, low, b_off: int, c_off: int, dtp, dt_bias, a_log, d_skip, zrows, z_off: int, cu_q, seq_slot, n_seqs: int, state, out,
+            chunked: bool = False) -> None:
+    """``S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x[t, c] B[t, n]``, ``y[t, c] = sum_n S[c, n] C[t, n] + D[c] x[t, c]``,
+    ``out[t, c] = T(y * silu(z[t, c]))`` with ``dt_c = softplus(dtp[t, c] + dt_bias[c])`` and ``A = -exp(a_log)``: ``xc [n,
+    inner]``, ``dtp [n, inner]`` float32; B and C are ``N`` columns of ``low [n, ld]`` (float32) from ``b_off`` / ``c_off``; z
+    ``inner`` columns of ``zrows [n, ld']`` (float32) from ``z_off``; ``state [slots, inner, N]`` float32 is read and left
+    advanced.  ``chunked``: a step of many tokens runs its chunks side by side (three launches)."""
+    n, inner = xc.shape
+    n_state = a_log.shape[1]
+    _need(xc, "xc", torch.float32)
+    _need(dtp, "dtp", torch.float32, (n, inner))
+    _need(low, "low", torch.float32, (n, None))
+    _need(zrows, "zrows", torch.float32, (n, None))
+    _need(a_log, "a_log", torch.float32, (inner, n_state))
+    for t, nm in ((dt_bias, "dt_bias"), (d_skip, "d_skip")):
+        _need(t, nm, torch.float32, (inner,))
+    _need(state, "state", torch.float32, (None, inner, n_state))
+    _need(out, "out", None, (n, inner))
+    for t, nm in ((cu_q, "cu_q"), (seq_slot, "seq_slot")):
+        _need(t, nm, torch.int32)
+    if min(b_off, c_off) < 0 or max(b_off, c_off) + n_state > low.shape[1] or z_off < 0 or z_off + inner > zrows.shape[1]:
+        raise KernelError("selscan: B, C or z columns outside their rows")
+    cht = n_chunks = 0
+    cstate = cdt = None
+    if chunked:
+        cht = max(SELSCAN_CHUNK_TOKENS, -(-n // 64 // 32) * 32)
+        n_chunks = n // cht + int(n_seqs)
+        cstate = torch.empty((n_chunks, inner, n_state), dtype=torch.float32, device=xc.device)
+        cdt = torch.empty((n_chunks, inner), dtype=torch.float32, device=xc.device)
+    _ok(selscan_lib().dryft_selscan(_act(out, "out"), _ptr(xc), _ptr(low), low.shape[1], int(b_off), int(c_off), _ptr(dtp), _ptr(dt_bias),
+                                    _ptr(a_log), _ptr(d_skip), _ptr(zrows), zrows.shape[1], int(z_off), _ptr(cu_q), _ptr(seq_slot),
+                                    int(n_seqs), cht, n_chunks, inner, n_state, _ptr(state), _ptr(cstate), _ptr(cdt), _ptr(out), _stream()),
+        f"selscan ({inner} channels, state {n_state})", n_kernels=3 if chunked else 1)

@@ -7,7 +7,7 @@ from .base import (
     CONNECTIONS, register_block, register_connection, register_embedding, register_ffn, register_head, register_mixer,
     register_norm, register_position,
 )
-from . import attention, block, diff_attention, embedding, ffn, hyper, latent_attention, moe, norm, pooled_attention, position, retention, rglru, ssd  # noqa: F401  (registration)
+from . import attention, block, diff_attention, embedding, ffn, hyper, latent_attention, moe, norm, pooled_attention, position, retention, rglru, selective_scan, side_by_side, ssd  # noqa: F401  (registration)
 from .linear import linear
 
 __all__ = [

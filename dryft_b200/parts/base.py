@@ -112,6 +112,10 @@ class Residual:
     # the streams, and the block that turns the streams into the rows the last norm and the head read
     conn: Optional[Any] = None
     closer: Optional[Any] = None
+    # ``x`` already normed by ``hn_norm`` (in the activation type): left by the kernel that formed ``x`` for the layer
+    # whose first norm that is, which then skips its own norm launch
+    hn: Optional[torch.Tensor] = None
+    hn_norm: Optional[Any] = None
 
 
 def fused_rms(norm) -> Optional[Tuple[torch.Tensor, float]]:

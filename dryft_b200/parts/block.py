@@ -213,3 +213,95 @@ class PostNormBlock:
             y = self.ffn.forward(h, ctx)
             h = self.norm_ffn.sum_norm(x, y, conn.keep, gate=conn.logits(h), gate_bias=conn.b)
         return Residual(x, h=h)
+
+
+@register_block("parallel")
+class ParallelBlock:
+    """One norm, read by the mixer and the feed-forward alike, whose results join a 32-bit stream together:
+
+        n = norm_mixer(x) ;  x <- x + mixer(n) + ffn(n)
+
+    ``res.x`` is float32 in both precisions.  The sum is one kernel (``csrc/stream_par.cu``): a mixer that offers
+    ``forward_terms`` (two mixers side by side) hands over its results unsummed with their factors, a routed feed-forward
+    whose weights are already inside its experts (``sums_plainly``) its ``top`` rows per token; the same kernel leaves the
+    stream normed for the layer that runs next when that layer's norm is known (``next_norm``), so a layer is one norm-less
+    chain of products and one sum.  There is no second norm (``norm_ffn`` must be None); a layer without a feed-forward
+    adds the mixer's result alone."""
+
+    takes_next_norm = True
+
+    def __init__(self, norm_mixer, mixer, norm_ffn, ffn):
+        if norm_ffn is not None:
+            raise ValueError("the 'parallel' arrangement has one norm: its feed-forward reads the mixer's normed input")
+        self.norm_mixer, self.mixer, self.norm_ffn, self.ffn = norm_mixer, mixer, None, ffn
+        K.stream_par_lib()
+
+    @staticmethod
+    def _plain(norm):
+        """``(factor, eps)`` of a norm that is ``x / sqrt(mean(x^2) + eps) * factor`` in 32-bit, rounded once; else None."""
+        get = getattr(norm, "plain_params", None)
+        return get() if callable(get) else None
+
+    def forward(self, res: Residual, ctx: StepContext, cache, state, owns_cache: bool = True, next_norm=None) -> Residual:
+        x = res.x
+        if x.dtype != torch.float32:
+            raise ValueError("the 'parallel' arrangement keeps its stream in float32; the embedding must start one")
+        if res.delta is not None:
+            x.add_(res.delta)
+        n = res.hn if (res.hn is not None and res.hn_norm is self.norm_mixer) else self.norm_mixer.forward(x)
+        terms = getattr(self.mixer, "forward_terms", None)
+        terms = terms(n, ctx, cache, state, owns_cache) if terms is not None else [(self.mixer.forward(n, ctx, cache, state, owns_cache), 1.0)]
+        rows, top = None, 0
+        if self.ffn is not None:
+            if getattr(self.ffn, "sums_plainly", False):
+                rows, top = self.ffn.forward_rows(n, ctx)
+            else:
+                terms = list(terms) + [(self.ffn.forward(n, ctx), 1.0)]
+        plain = self._plain(next_norm) if next_norm is not None else None
+        hn = None
+        if plain is not None:
+            hn = torch.empty(x.shape, dtype=self.mixer.rt.dtype, device=x.device)
+            K.stream_sum(x, terms, rows=rows, top=top, norm_w=plain[0], eps=plain[1], h=hn)
+        else:
+            K.stream_sum(x, terms, rows=rows, top=top)
+        return Residual(x, hn=hn, hn_norm=next_norm if hn is not None else None)
+
+
+@register_connection("loop_mix")
+class LoopMix:
+    """How a stretch of layers that runs several times is entered: ``x <- W [x | x0] + step[t]`` with ``x0`` the embedding's
+    output, ``W`` a ``[size, 2 size]`` matrix (the stream's columns first) and ``step`` one vector per pass ``t``.  The two
+    32-bit rows are rounded side by side as the product's operand; the product's 32-bit sums, plus the pass's vector,
+    are the new stream.  ``params``: ``size``, ``times``, ``matrix`` and ``steps`` (tensor names behind the prefix)."""
+
+    @staticmethod
+    def tensors(params: Mapping, prefix: str) -> Dict[str, TensorInfo]:
+        size = int(params["size"])
+        return {prefix + params.get("matrix", "in"): TensorInfo((size, 2 * size), "matrix"),
+                prefix + params.get("steps", "step"): TensorInfo((int(params["times"]), size), "vector", False, 0.0)}
+
+    def __init__(self, params: Mapping, prefix: str, weights, rt: Runtime):
+        self.rt = rt
+        self.size, self.times = int(params["size"]), int(params["times"])
+        self.w = weights.load(prefix + params.get("matrix", "in"), "matrix")
+        self.steps = weights.load(prefix + params.get("steps", "step"), "vector").to(torch.float32).contiguous()   # [times, size]
+        K.stream_par_lib()
+
+    def enter(self, res: Residual, x0: torch.Tensor, number: int, next_norm=None) -> Residual:
+        if not 0 <= number < self.times:
+            raise ValueError(f"loop_mix: pass {number} of {self.times}")
+        x = res.x
+        if x.dtype != torch.float32 or x0 is None or x0.dtype != torch.float32:
+            raise ValueError("loop_mix joins 32-bit streams; the embedding must start one")
+        if res.delta is not None:
+            x.add_(res.delta)
+        pair = torch.empty((x.shape[0], 2 * self.size), dtype=self.rt.dtype, device=x.device)
+        K.pack_pair(x, x0, pair)
+        y = linear(pair, self.w, self.rt, out_dtype=torch.float32)
+        plain = ParallelBlock._plain(next_norm) if next_norm is not None else None
+        if plain is None:
+            K.stream_sum(y, vec=self.steps[number])
+            return Residual(y)
+        hn = torch.empty(y.shape, dtype=self.rt.dtype, device=y.device)
+        K.stream_sum(y, vec=self.steps[number], norm_w=plain[0], eps=plain[1], h=hn)
+        return Residual(y, hn=hn, hn_norm=next_norm)

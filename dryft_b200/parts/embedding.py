@@ -106,10 +106,21 @@ class LMHead:
                 del other
         else:
             self.weight = weights.load(name, "matrix")
+        # ``params["softcap"]``: logits <- cap * tanh(logits / cap), in 32-bit, after the product
+        self.softcap = float(params["softcap"]) if params.get("softcap") is not None else None
+        if self.softcap is not None:
+            if not self.softcap > 0.0:
+                raise ValueError(f"lm_head: softcap must be positive, got {self.softcap}")
+            K.stream_par_lib()
+
+    def _cap(self, logits: torch.Tensor) -> torch.Tensor:
+        if self.softcap is not None:
+            K.softcap(logits, self.softcap)
+        return logits
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         """32-bit logits ``[rows, vocab]``."""
-        return linear(h, self.weight, self.rt, out_dtype=torch.float32)
+        return self._cap(linear(h, self.weight, self.rt, out_dtype=torch.float32))
 
     def can_fuse(self, n_rows: int, norm) -> bool:
         rt = self.rt
@@ -126,7 +137,7 @@ class LMHead:
             K.fused_product(x, self.weight, out, small_m_max=small, xw_in=xw, norm_w=norm_w, ss_in=ss, ss_parts=ss_parts, eps=eps, pdl=self.rt.pdl)
         else:
             K.fused_product(x, self.weight, out, small_m_max=small, norm_w=norm_w, ss_in=ss, ss_parts=ss_parts, eps=eps, pdl=self.rt.pdl)
-        return out
+        return self._cap(out)
 
 
 @register_embedding("pair_embedding")

@@ -7,6 +7,7 @@ With ``H`` heads, per head ``d`` unrotated and ``r`` rotated query/key dims, val
     [c_raw | k_rot] = W_dkv h ;  c = rmsnorm(c_raw) ;  k_rot rotated at the token's position, one vector for all heads
     per head:  k = W_uk c ,  v = W_uv c ;  score(i, j) = (q_plain . k + q_rot . k_rot) * scale ,  0 <= i - j < window
     o = softmax(score) v ;  o <- o * sigmoid(W_g h)_head  ->  @ W_o.T
+    (``sink``: the softmax's denominator of head ``h`` also holds ``exp(sink_h)``, a learned number without key or value)
 
 Only ``[c | k_rot]`` is cached, one row per token for all heads (a keys-only cache group).  The per-head key and value
 matrices are folded into the query and the output: ``q_lat = W_uk^T q_plain`` before attention, ``o = W_uv o_lat`` after,
@@ -32,7 +33,7 @@ from .base import POSITIONS, Runtime, StepContext, TensorInfo, register_mixer
 from .linear import linear
 
 _ROLES = {"dq": "q_down.weight", "dq_norm": "q_down.norm", "uq": "q_up.weight", "dkv": "kv_down.weight", "dkv_norm": "kv_down.norm",
-          "uk": "k_up.weight", "uv": "v_up.weight", "gate": "g_proj.weight", "o": "o_proj.weight"}
+          "uk": "k_up.weight", "uv": "v_up.weight", "gate": "g_proj.weight", "o": "o_proj.weight", "sink": "sink"}
 
 
 def _names(params: Mapping, prefix: str) -> Dict[str, str]:
@@ -53,6 +54,8 @@ class LatentAttention:
              nm["uv"]: TensorInfo((h * dv, kr), "matrix"), nm["o"]: TensorInfo((w, h * dv), "matrix")}
         if params.get("gate", True):
             t[nm["gate"]] = TensorInfo((h, w), "matrix")
+        if params.get("sink", False):
+            t[nm["sink"]] = TensorInfo((h,), "vector", False, 0.0)
         return t
 
     def __init__(self, params: Mapping, prefix: str, weights, rt: Runtime):
@@ -86,6 +89,7 @@ class LatentAttention:
         self.w_o = weights.load(nm["o"], "matrix")
         self.dq_norm_w = weights.load(nm["dq_norm"], "vector")
         self.dkv_norm_w = weights.load(nm["dkv_norm"], "vector")
+        self.sink = weights.load(nm["sink"], "vector").to(torch.float32).contiguous() if params.get("sink", False) else None
         H, d, dv, kr = self.n_heads, self.qk_dim, self.v_dim, self.kv_rank
         w_uk = weights.load(nm["uk"], "matrix")      # [H*d, kr]
         w_uv = weights.load(nm["uv"], "matrix")      # [H*dv, kr]
@@ -98,9 +102,15 @@ class LatentAttention:
         hd = d + self.rot_dim
         self.use_prompt_tc = rt.is_bf16 and hd % 16 == 0 and hd <= 256 and dv <= hd and rt.page_size == 64
         self.uses_fresh_steps = self.use_prompt_tc
+        if self.use_prompt_tc and self.sink is not None:
+            # with a sink the prompt kernel is the one that opens its softmax with it (values padded to the key size)
+            self.use_prompt_tc = self.uses_fresh_steps = K.pool_attention_prefill_supported(hd, hd, 1, rt.page_size)
         if self.use_prompt_tc:
             self.w_ukv = torch.cat([w_uk, w_uv], dim=0).contiguous()      # [H*d + H*dv, kr]
-            K.attention_prefill_lib(hd, 1, rt.page_size)
+            if self.sink is not None:
+                K.pool_attention_prefill_lib(hd, hd, 1, rt.page_size)
+            else:
+                K.attention_prefill_lib(hd, 1, rt.page_size)
 
     def kv_need(self) -> KVNeed:
         return KVNeed(1, self.kv_rank + self.rot_dim, self.window, values=False)
@@ -132,8 +142,12 @@ class LatentAttention:
             K.latent_expand_store(q, kv, H * d, proj, self.dkv_off + kr, self.position.inv_freq, self.position.interleaved, ctx.cu_q,
                                   ctx.seq_slot, ctx.n_seqs, ctx.tok_slot, ctx.tok_pos, table, q_full, k_s, v_s, d, r, dv, inv_freq_lo=lo)
             o_pad = torch.empty((n, H * hd), dtype=h.dtype, device=dev)
-            K.attn_prefill(q_full, k_s, v_s, table, ctx.tile_tok0, ctx.tile_rows, ctx.tok_slot, ctx.tok_pos, o_pad, ctx.n_tiles,
-                           self.scale, self.window)
+            if self.sink is not None:
+                K.pool_attn_prefill(q_full, k_s, v_s, table, None, self.sink, ctx.tile_tok0, ctx.tile_rows, ctx.tok_slot, ctx.tok_pos,
+                                    o_pad.view(n, H, hd), ctx.n_tiles, self.scale, self.window or (1 << 30), 0)
+            else:
+                K.attn_prefill(q_full, k_s, v_s, table, ctx.tile_tok0, ctx.tile_rows, ctx.tok_slot, ctx.tok_pos, o_pad, ctx.n_tiles,
+                               self.scale, self.window)
             out = torch.empty((n, H * dv), dtype=h.dtype, device=dev)
             K.head_gate_rows(o_pad, proj if self.has_gate else None, self.gate_col, out, H, dv)
             return linear(out, self.w_o, self.rt)
@@ -149,7 +163,7 @@ class LatentAttention:
         o_lat = torch.empty((H, n, kr), dtype=h.dtype, device=dev)
         K.latent_attn_rows(q_lat, q, d, cache.k, cache.page_table, ctx.tok_slot, ctx.tok_pos, self.position.inv_freq,
                            self.position.interleaved, o_lat, kr, r, self.scale, self.window,
-                           inv_freq_lo=lo, n_splits=self._n_splits(n, ctx.max_kv))
+                           inv_freq_lo=lo, n_splits=self._n_splits(n, ctx.max_kv), sink=self.sink)
         out = torch.empty((n, H * dv), dtype=h.dtype, device=dev)
         if own:
             K.latent_unfold_o(o_lat, self.w_uv_t, proj if self.has_gate else None, self.gate_col, out)

@@ -16,6 +16,12 @@ choice is ``csrc/moe.cu:moe_route``.  The experts run assignment by assignment f
 products over the tokens sorted by expert for prompts in bfloat16 (``csrc/moe_grouped.cu``).  The weighted sum is left
 to the caller through ``forward_parts`` (a layer that normalises the sum forms it inside its norm kernel in 32-bit);
 ``forward`` forms it itself.  ``params["names"]`` maps roles to tensor names behind the prefix.
+
+``score="sigmoid"``: an expert's score is the sigmoid of its own logit (no softmax over the experts).  ``weight_input``: the
+chosen expert's weight multiplies its INPUT, ``out = sum_k expert_k(w_k h)``, not its output; since the first products are
+linear, the weight is applied to their 32-bit sums, before the activation.  ``activation="clamped"`` (with ``limit``,
+``alpha``, ``up_offset``): ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``, ``down(g * sigmoid(alpha g) * (u +
+up_offset))``.
 """
 
 from __future__ import annotations
@@ -44,7 +50,7 @@ class MoE:
     def tensors(params: Mapping, prefix: str) -> Dict[str, TensorInfo]:
         w, f, e = params["hidden_size"], params["intermediate_size"], params["experts"]
         nm = _names(params)
-        gated = params.get("activation", "swiglu") == "swiglu"
+        gated = params.get("activation", "swiglu") in ("swiglu", "clamped")
         t = {prefix + nm["router"]: TensorInfo((e, w), "matrix")}
         if params.get("router_bias"):
             t[prefix + nm["router_bias"]] = TensorInfo((e,), "vector", False, 0.0)
@@ -77,9 +83,24 @@ class MoE:
         if self.experts % self.groups or not 1 <= self.keep <= self.groups or not 1 <= self.top <= self.experts:
             raise ValueError(f"moe: {self.experts} experts, {self.groups} groups, keep {self.keep}, top {self.top} do not go together")
         act = params.get("activation", "swiglu")
-        if act not in ("swiglu", "relu2"):
-            raise ValueError(f"moe: activation must be 'swiglu' or 'relu2', got {act!r}")
-        self.gated = act == "swiglu"
+        if act not in ("swiglu", "relu2", "clamped"):
+            raise ValueError(f"moe: activation must be 'swiglu', 'relu2' or 'clamped', got {act!r}")
+        self.gated = act in ("swiglu", "clamped")
+        self.score = params.get("score", "softmax")
+        if self.score not in ("softmax", "sigmoid"):
+            raise ValueError(f"moe: score must be 'softmax' or 'sigmoid', got {self.score!r}")
+        # the weight on the expert's input; the clamped activation's constants (a plain gated expert is the clamped one
+        # with no limit, alpha 1 and no offset, so both run through the same kernel mode when the weight is on the input)
+        self.weight_input = bool(params.get("weight_input", False))
+        self.clamped = act == "clamped"
+        self.limit = None if params.get("limit") is None else float(params["limit"])
+        self.alpha = float(params.get("alpha", 1.0)) if self.clamped else 1.0
+        self.up_offset = float(params.get("up_offset", 0.0)) if self.clamped else 0.0
+        if not self.clamped:
+            self.limit = None
+        if self.weight_input and not self.gated:
+            raise ValueError("moe: a weight on the expert's input is served for gated experts")
+        self.sums_plainly = self.weight_input      # the experts' rows are summed as they are (the weights are inside)
         nm = _names(params)
         # The router's logits are 32-bit sums.  In the bfloat16 path its operands are the bfloat16 activations and the
         # weight as stored (their products are exact in 32-bit), multiplied by the tensor-core products with 32-bit
@@ -131,10 +152,10 @@ class MoE:
         if (n <= self.ROUTE_ROWS_MAX and self.w_router.dtype == h.dtype and self.w_router.numel() <= self.ROUTE_ROWS_MAX_WEIGHTS
                 and K.moe_route_rows_supported(self.hidden, self.experts, self.groups, h.element_size())):
             K.moe_route_rows(h, self.w_router, self.groups, self.keep, self.top, idx, wts, renorm=self.renorm,
-                             bias=self.router_bias)   # one launch
+                             bias=self.router_bias, score=self.score)   # one launch
             return idx, wts
         logits = linear(h, self.w_router, self.rt, out_dtype=torch.float32)
-        K.moe_route(logits, self.groups, self.keep, self.top, idx, wts, renorm=self.renorm, bias=self.router_bias)
+        K.moe_route(logits, self.groups, self.keep, self.top, idx, wts, renorm=self.renorm, bias=self.router_bias, score=self.score)
         return idx, wts
 
     def absorb_rows(self, w: torch.Tensor) -> bool:
@@ -164,16 +185,36 @@ class MoE:
     def forward_parts(self, h: torch.Tensor, ctx: StepContext) -> Tuple[torch.Tensor, torch.Tensor, int]:
         """``(y [n*top, hidden], wts [n, top], top)``: row ``n*top + k`` is the output of token ``n``'s k-th expert, not yet
         weighted."""
+        y, wts = self._experts(h)
+        if self.weight_input:      # the weights are inside the experts already: the rows are summed as they are
+            wts = torch.ones_like(wts)
+        return y, wts, self.top
+
+    def forward_rows(self, h: torch.Tensor, ctx: StepContext) -> Tuple[torch.Tensor, int]:
+        """``(y [n*top, hidden], top)`` for experts whose weights are on their input (``sums_plainly``): the caller adds a
+        token's ``top`` rows as they are."""
+        if not self.sums_plainly:
+            raise ValueError("moe: forward_rows is for experts weighted on their input; use forward_parts")
+        return self._experts(h)[0], self.top
+
+    def _experts(self, h: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         n = h.shape[0]
         idx, wts = self.route(h)
         y = torch.empty((n * self.top, self.hidden), dtype=h.dtype, device=h.device)
+        special = self.weight_input or self.clamped      # the kernel mode with a weight on the input and the clamped activation
+        in_w = wts if self.weight_input else (torch.ones_like(wts) if special else None)
         if self.use_grouped and n >= self.GROUPED_MIN_TOKENS:
-            K.moe_grouped(h, self.w_gate_up, self.w_down, idx, y, gated=self.gated)
+            K.moe_grouped(h, self.w_gate_up, self.w_down, idx, y, gated=self.gated, in_w=in_w, limit=self.limit, alpha=self.alpha,
+                          up_offset=self.up_offset)
         else:
             act = torch.empty((n * self.top, self.inter), dtype=h.dtype, device=h.device)
-            K.moe_rows(h, self.w_gate_up, idx, act, "gate_up" if self.gated else "up_relu2")
+            if special:
+                K.moe_rows(h, self.w_gate_up, idx, act, "gate_up_clamp", in_w=in_w, limit=self.limit, alpha=self.alpha,
+                           up_offset=self.up_offset)
+            else:
+                K.moe_rows(h, self.w_gate_up, idx, act, "gate_up" if self.gated else "up_relu2")
             K.moe_rows(act, self.w_down, idx, y, "down")
-        return y, wts, self.top
+        return y, wts
 
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         y, wts, top = self.forward_parts(h, ctx)

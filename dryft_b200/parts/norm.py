@@ -70,6 +70,13 @@ class OffsetRMSNorm:
         self.weight = weights.load(prefix + params.get("name", "weight"), "vector")  # float32 [size]
         self._factor: Optional[torch.Tensor] = None   # offset + weight, formed when ``sum_norm`` first asks
 
+    def plain_params(self):
+        """``(factor, eps)``: this norm is ``x / sqrt(mean(x^2) + eps) * factor`` in 32-bit, rounded once -- what a kernel that
+        has the row in hand anyway (the sum that forms the stream) may compute on the side."""
+        if self._factor is None:
+            self._factor = self.weight if self.offset == 0.0 else (self.weight + self.offset)
+        return self._factor, self.eps
+
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> torch.Tensor:
         n = n_rows if n_rows is not None else (rows.numel() if rows is not None else x.shape[0])
         out = torch.empty((n, self.size), dtype=self.rt.dtype, device=x.device)

@@ -12,7 +12,13 @@ Per step, with ``h`` the mixer's input:
     the query at position i sees the tokens j with 0 <= i - j < window and the pooled rows of the blocks b with
           b * pool + pool - 1 <= i - window; scores ``(q . k) * scale``; tokens and blocks share one softmax whose
           denominator also holds ``exp(sink_head)`` (``sink``: a number per head without key or value)
+    (``head_gate``: head ``h``'s output is multiplied by ``sigmoid(W_g h)_h``, one number per head, ``W_g [heads, hidden]``
+          riding in the input product)
     out = W_o (heads concatenated)
+
+``proj_norm``: q and k pass an RMS norm over the WHOLE projection (all heads' rows at once, weights ``q_norm [heads * qk_dim]``
+and ``k_norm [kv_heads * qk_dim]``, ``eps`` inside the root) before the rotation.  The rotation's layout is the position
+part's (``half``: dims ``i`` and ``i + R/2``; ``interleaved``: dims ``2i`` and ``2i + 1``).
 
 Without a ``window`` every earlier token is seen and there are no pooled rows.  A run step that borrows another's cache uses
 its own queries, window, pool, scale and sink over the owner's rows; when it summarises the same blocks as the owner it
@@ -35,7 +41,8 @@ from .base import POSITIONS, Runtime, StepContext, TensorInfo, register_mixer
 from .linear import linear
 
 _ROLES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight", "q_bias": "q_proj.bias",
-          "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "sink": "sink"}
+          "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "sink": "sink", "q_norm": "q_norm.weight", "k_norm": "k_norm.weight",
+          "gate": "g_proj.weight"}
 NO_WINDOW = 1 << 30   # "every earlier token" as a window size
 
 
@@ -63,6 +70,12 @@ class PooledWindowAttention:
                 t[nm["v_bias"]] = TensorInfo((nkv * dv,), "vector", False, 0.0)
         if params.get("sink", False):
             t[nm["sink"]] = TensorInfo((nh,), "vector", False, 0.0)
+        if params.get("proj_norm", False):
+            t[nm["q_norm"]] = TensorInfo((nh * d,), "vector")
+            if own:
+                t[nm["k_norm"]] = TensorInfo((nkv * d,), "vector")
+        if params.get("head_gate", False):
+            t[nm["gate"]] = TensorInfo((nh, w), "matrix")
         return t
 
     def __init__(self, params: Mapping, prefix: str, weights, rt: Runtime):
@@ -82,11 +95,19 @@ class PooledWindowAttention:
         self.own_kv = bool(params.get("own_kv", True))
         self.q_dim, self.o_dim = self.n_heads * self.qk_dim, self.n_heads * self.v_dim
         nm = _names(params, prefix)
+        self.head_gate = bool(params.get("head_gate", False))
+        names, rows = [nm["q"]], [self.q_dim]
         if self.own_kv:
-            self.w_in = weights.load_fused([nm["q"], nm["k"], nm["v"]],
-                                           [self.q_dim, self.n_kv * self.qk_dim, self.n_kv * self.v_dim], self.hidden)
-        else:
-            self.w_in = weights.load(nm["q"], "matrix")
+            names += [nm["k"], nm["v"]]
+            rows += [self.n_kv * self.qk_dim, self.n_kv * self.v_dim]
+        self.gate_col = sum(rows)
+        if self.head_gate:                 # the gate's logits are columns of the input product
+            names.append(nm["gate"])
+            rows.append(self.n_heads)
+        self.w_in = weights.load_fused(names, rows, self.hidden) if len(names) > 1 else weights.load(nm["q"], "matrix")
+        self.proj_norm = bool(params.get("proj_norm", False))
+        self.q_norm_w = weights.load(nm["q_norm"], "vector") if self.proj_norm else None
+        self.k_norm_w = weights.load(nm["k_norm"], "vector") if self.proj_norm and self.own_kv else None
         self.w_o = weights.load(nm["o"], "matrix")
         bias = bool(params.get("bias", False))
         self.q_bias = weights.load(nm["q_bias"], "vector") if bias else None
@@ -96,8 +117,13 @@ class PooledWindowAttention:
         self.side, self.side_out = None, None      # (first column, columns) of rows that ride with the input product
         pos: PartSpec = params.get("position") or PartSpec("none")
         self.position = POSITIONS.get(pos.kind)(pos.params, self.qk_dim, rt)
-        if getattr(self.position, "interleaved", False):
-            raise ValueError("pooled_window_attention: its kernels rotate dims j and j + R/2 together")
+        self.interleaved = bool(getattr(self.position, "interleaved", False))
+        # the per-token preparation with one block a token takes the norm over whole projections and both rotation layouts
+        self.prep_by_token = self.proj_norm or self.interleaved
+        if self.prep_by_token and bias:
+            raise ValueError("pooled_window_attention: biases do not go with a norm over the whole projection or the interleaved layout")
+        if self.head_gate:
+            K.latent_attn_lib()            # the per-head gate kernel lives beside the other gated attention
         self.rot = int(getattr(self.position, "rotary_dim", 0) or 0) if getattr(self.position, "inv_freq", None) is not None else 0
         K.pool_attention_lib(self.qk_dim, self.v_dim, self.group)   # build (or find) the kernels of this head shape now
         self.use_prefill_kernel = rt.is_bf16 and K.pool_attention_prefill_supported(self.qk_dim, self.v_dim, self.group)
@@ -139,9 +165,15 @@ class PooledWindowAttention:
             self.side_out = proj[:, self.side[0]:self.side[0] + self.side[1]]
         q = torch.empty((n, self.n_heads, self.qk_dim), dtype=h.dtype, device=dev)
         pos = self.position
-        K.pool_attn_prep(proj, self.q_bias, self.k_bias, self.v_bias, pos.inv_freq if self.rot else None,
-                         getattr(pos, "inv_freq_lo", None) if self.rot else None, self.rot, ctx.tok_slot, ctx.tok_pos, q, cache.k,
-                         cache.v, cache.page_table, self.n_heads, self.n_kv, self.eps if self.unit_norm else -1.0, owns_cache)
+        if self.prep_by_token:
+            K.pool_attn_prep_tok(proj, self.q_norm_w, self.k_norm_w, self.eps, pos.inv_freq if self.rot else None,
+                                 getattr(pos, "inv_freq_lo", None) if self.rot else None, self.rot, self.interleaved, ctx.tok_slot,
+                                 ctx.tok_pos, q, cache.k, cache.v, cache.page_table, self.n_heads, self.n_kv,
+                                 self.eps if self.unit_norm else -1.0, owns_cache)
+        else:
+            K.pool_attn_prep(proj, self.q_bias, self.k_bias, self.v_bias, pos.inv_freq if self.rot else None,
+                             getattr(pos, "inv_freq_lo", None) if self.rot else None, self.rot, ctx.tok_slot, ctx.tok_pos, q, cache.k,
+                             cache.v, cache.page_table, self.n_heads, self.n_kv, self.eps if self.unit_norm else -1.0, owns_cache)
         pooled = None
         if self.pool:
             pc = cache.pooled
@@ -163,4 +195,7 @@ class PooledWindowAttention:
                 part_ml = torch.empty((n, self.n_heads, s, 2), dtype=torch.float32, device=dev)
             K.pool_attn_rows(q, cache.k, cache.v, cache.page_table, pooled, self.sink, ctx.tok_slot, ctx.tok_pos, o, self.scale,
                              self.size, self.pool, s, part_o, part_ml)
-        return linear(o.view(n, self.o_dim), self.w_o, self.rt)
+        o = o.view(n, self.o_dim)
+        if self.head_gate:
+            K.head_gate_rows(o, proj, self.gate_col, o, self.n_heads, self.v_dim)     # in place: an entry reads only itself
+        return linear(o, self.w_o, self.rt)

@@ -44,7 +44,8 @@ class Rope:
     ``2j`` and ``2j + 1``); the mixers whose kernels take both read ``interleaved``.  ``params["freq"]``: ``"float32"``
     (the reference's expression, evaluated in 32-bit; the default) or ``"rounded_once"`` (``theta^(-2j/R)`` evaluated in
     64-bit and rounded to 32-bit once; what that rounding drops is kept as ``inv_freq_lo`` for kernels that take the pair).
-    ``params["scaling"]`` (needs ``freq="rounded_once"``): a mapping ``factor, low, high, original`` that slows long waves: with
+    ``params["scaling"]`` (needs ``freq="rounded_once"``): ``{"factor": s}`` alone divides every frequency by ``s`` (linear
+    scaling); otherwise a mapping ``factor, low, high, original`` that slows long waves: with
     the wavelength ``l = 2 pi / f``, ``f`` stays where ``l < original / high``, becomes ``f / factor`` where ``l > original /
     low``, and in between ``(1 - s) f / factor + s f`` with ``s = (original / l - low) / (high - low)``."""
 
@@ -62,7 +63,13 @@ class Rope:
         if params.get("freq", "float32") == "rounded_once":
             exact = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -torch.arange(0, r, 2, dtype=torch.float64) / r)
             if params.get("scaling") is not None:
-                exact = scale_by_wavelength(exact, params["scaling"])
+                sc = params["scaling"]
+                if set(sc) == {"factor"}:      # linear scaling: every frequency divided by the same number
+                    if not float(sc["factor"]) > 0:
+                        raise ValueError(f"rope scaling: factor must be positive, got {dict(sc)}")
+                    exact = exact / float(sc["factor"])
+                else:
+                    exact = scale_by_wavelength(exact, sc)
             inv_freq = exact.to(torch.float32)
             self.inv_freq_lo = (exact - inv_freq.to(torch.float64)).to(torch.float32).to(rt.device)
         else:

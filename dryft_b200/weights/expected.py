@@ -21,11 +21,14 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, TensorInfo]:
     for layer in spec.layers:
         add(NORMS.get(layer.norm_mixer.kind).tensors(layer.norm_mixer.params, layer.norm_mixer_prefix))
         add(MIXERS.get(layer.mixer.kind).tensors(layer.mixer.params, layer.mixer_prefix))
-        if layer.ffn is not None:
+        if layer.norm_ffn is not None:
             add(NORMS.get(layer.norm_ffn.kind).tensors(layer.norm_ffn.params, layer.norm_ffn_prefix))
+        if layer.ffn is not None:
             add(FFNS.get(layer.ffn.kind).tensors(layer.ffn.params, layer.ffn_prefix))
         for e in layer.extra:
             add(FAMILIES[e.family].get(e.spec.kind).tensors(e.spec.params, e.prefix))
+    for j in spec.joints:
+        add(FAMILIES[j.family].get(j.spec.kind).tensors(j.spec.params, j.prefix))
     add(NORMS.get(spec.final_norm.kind).tensors(spec.final_norm.params, spec.final_norm_prefix))
     add(HEADS.get(spec.head.kind).tensors(spec.head.params, spec.head_prefix))
     return out
