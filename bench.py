@@ -194,9 +194,10 @@ def prefill_time(eng, tokens, iters, seed):
 
 # ----------------------------------------------------------------------------- two designs at equal size
 def compare_arm(args, warmup) -> int:
-    """Prefill and decode throughput of Tevovik, Vobusun or Mogelix shapes, each beside the shape of equal size (same width,
-    layers, heads, vocabulary; the dense intermediate size is the expert size times the experts a token uses, or the
-    Vobusun feed-forward's own size; a Mogelix shape stands beside the Tevovik shape of its sizes).  One JSON line."""
+    """Prefill and decode throughput of Tevovik, Vobusun, Mogelix or Kerirax shapes, each beside the shape of equal size (same
+    width, layers, heads, vocabulary; the dense intermediate size is the expert size times the experts a token uses, or the
+    Vobusun feed-forward's own size; a Mogelix shape stands beside the Tevovik shape of its sizes, a Kerirax shape beside
+    the Mogelix shape of its sizes).  One JSON line."""
     import torch
 
     from dryft_b200.config import config_from_dict, preset
@@ -387,8 +388,9 @@ def main() -> int:
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--compare", default=None, metavar="SHAPE[,SHAPE]",
                     help="instead of the default workload: prefill (2,048 tokens) and decode (batch 1 and 8) of these Tevovik, "
-                         "Vobusun or Mogelix presets, each beside the preset of equal size (tevovik-1k, tevovik-2k, vobusun-1k, "
-                         "vobusun-2k beside dense Qwen3 shapes; mogelix-1k, mogelix-2k beside the Tevovik shapes)")
+                         "Vobusun, Mogelix or Kerirax presets, each beside the preset of equal size (tevovik-1k, tevovik-2k, vobusun-1k, "
+                         "vobusun-2k beside dense Qwen3 shapes; mogelix-1k, mogelix-2k beside the Tevovik shapes; kerirax-1k, "
+                         "kerirax-2k beside the Mogelix shapes)")
     ap.add_argument("--small-m-max", type=int, default=None,
                     help="rows up to which decode products stream weights themselves (the engine's default if not given)")
     ap.add_argument("--engine-opt", action="append", default=[], metavar="NAME=VALUE",

@@ -167,6 +167,40 @@ PRESETS.update({
 EQUAL_SIZE.update({"mogelix-1k": "tevovik-1k", "mogelix-2k": "tevovik-2k"})
 
 
+def _kerirax(width: int, heads: int, kv_heads: int, dim: int, inner: int, state: int, dt_rank: int, q_rank: int, kv_rank: int,
+             rot_dim: int, experts: int, ff: int, top: int, vocab: int, stretch: int, times: int, tail: int) -> dict:
+    """A Kerirax ``config.json``: a stretch of ``stretch`` layers run ``times`` times, then ``tail`` more layers; every third
+    layer is attention over latents, the others two mixers side by side.  The first layer's feed-forward is dense (the size
+    of the experts a token uses plus one), the others are routed."""
+    rot = {"dims": dim, "base": 500000.0, "scaling": {"factor": 8.0}}
+    pair = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "rot": rot}, "left_scale": 1.0,
+            "right": {"inner": inner, "state": state, "dt_rank": dt_rank, "conv": 4}, "right_scale": 1.0}
+    lat = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": dim, "q_rank": q_rank, "kv_rank": kv_rank,
+           "scale": (dim + rot_dim) ** -0.5, "rot": {"dims": rot_dim, "base": 20000.0}}
+    out = []
+    for i in range(stretch + tail):
+        mlp = {"kind": "dense", "ff": ff * (top + 1)} if i == 0 else \
+            {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": experts, "top": top}}
+        out.append({"type": "latent_attention", "mixer": lat, "mlp": mlp} if i % 3 == 1 else {"type": "parallel", "mixer": pair, "mlp": mlp})
+    return {"architecture": "Kerirax", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
+            "logit_softcap": 30.0, "loop": {"start": 0, "stop": stretch, "times": times}, "layers": out}
+
+
+# Kerirax shapes with layers the size of a real model's, and beside each the closest design at equal size: the Mogelix shape
+# of the same width, number of layer runs (a layer that runs three times counts three times), head counts and size, expert
+# count and size, experts a token uses and vocabulary (its state-space layers carry a matrix state per head where the
+# selective scan carries a vector per channel).
+PRESETS.update({
+    "kerirax-tiny": _kerirax(width=64, heads=4, kv_heads=2, dim=16, inner=96, state=8, dt_rank=8, q_rank=24, kv_rank=32, rot_dim=8,
+                             experts=6, ff=32, top=2, vocab=256, stretch=2, times=2, tail=1),
+    "kerirax-1k": _kerirax(width=1024, heads=8, kv_heads=2, dim=128, inner=2048, state=16, dt_rank=64, q_rank=384, kv_rank=256,
+                           rot_dim=64, experts=32, ff=512, top=4, vocab=32768, stretch=2, times=3, tail=2),
+    "kerirax-2k": _kerirax(width=2048, heads=16, kv_heads=4, dim=128, inner=4096, state=16, dt_rank=128, q_rank=768, kv_rank=512,
+                           rot_dim=64, experts=64, ff=768, top=8, vocab=65536, stretch=3, times=3, tail=3),
+})
+EQUAL_SIZE.update({"kerirax-1k": "mogelix-1k", "kerirax-2k": "mogelix-2k"})
+
+
 def preset(name: str) -> dict:
     if name not in PRESETS:
         raise KeyError(f"unknown preset {name!r}; known: " + ", ".join(sorted(PRESETS)))

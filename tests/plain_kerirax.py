@@ -185,7 +185,7 @@ def expert(h: torch.Tensor, w: Mapping[str, torch.Tensor], pre: str, limit: floa
 
 def moe_ffn(h: torch.Tensor, mlp: Mapping, w: Mapping[str, torch.Tensor], pre: str) -> torch.Tensor:
     idx, wts = router_choice(h, mlp, w, pre)
-    limit = float(mlp["expert"]["limit"])
+    limit = float(mlp["expert"]["limit"]) if mlp["expert"].get("limit") is not None else math.inf
     out = torch.zeros(h.shape[0], w[pre + "e0.down"].shape[0], dtype=F)
     for t in range(h.shape[0]):
         for k in range(idx.shape[1]):
