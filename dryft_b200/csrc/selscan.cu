@@ -20,8 +20,11 @@
 //                     S_start(k+1) = exp(A * sum_k) S_start(k) + S_own(k), which turns the chunks' own states into their
 //                     start states and leaves the sequence's final state in the slot; <MODE 2> every chunk again from its
 //                     start state, writing the output.
-// A channel's N states are spread over `lpc` neighbouring lanes (a power of two up to 32), NR states a lane; the next
-// token's operands are requested before the current token's arithmetic.  Sequences with slot -1 (padding) are skipped.
+// A thread owns a channel while its N states fit sixteen registers; beyond that they are spread over `lpc` neighbouring lanes
+// (a power of two up to 32), NR neighbouring states a lane.  Tokens go by tiles of eight: the tile's B and C rows are staged
+// in shared memory (every channel reads them, 16 bytes at a time), and a thread asks for its channel's step sizes, inputs
+// and gates of all eight tokens before it uses the first, forms softplus, dt x, D x and silu(z) once per token and parks
+// them in shared memory, so that the loop over the states is a product, an exp2, and three multiply-adds per state.  Sequences with slot -1 (padding) are skipped.
 // No block waits on another block.
 #include "common.cuh"
 #include <math.h>
@@ -42,12 +45,28 @@ __device__ __forceinline__ bool chunk_of(const int* __restrict__ cu_q, int n_seq
   return false;
 }
 
+constexpr int TILE = 8;        // tokens whose operands are staged at once
+
+// exp2 of a number that is never positive: one instruction (results below the normal range flush to zero, which is what a
+// decay that small is)
+__device__ __forceinline__ float exp2_neg(float v) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+
+// A lane owns the NR neighbouring states n = sub * NR .. sub * NR + NR - 1 of its channel (NP = NR * lpc >= N of them exist
+// in the staged rows; those beyond N hold zeros there and in A2 and S, so they stay zero without a test).
 template <typename T, int MODE, int NR>
 __global__ void __launch_bounds__(SCAN_THREADS) selscan_kernel(
     const float* __restrict__ xc, const float* __restrict__ low, int low_ld, int b_off, int c_off, const float* __restrict__ dtp,
     const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ Dp, const float* __restrict__ zrows,
     int z_ld, int z_off, const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int n_seqs, int cht, int inner, int N,
     int lpc, float* __restrict__ state, float* __restrict__ cstate, float* __restrict__ cdt, T* __restrict__ out) {
+  extern __shared__ __align__(16) float sm[];
+  const int NP = NR * lpc;
+  float* bc = sm;                               // [TILE][2][NP]: B and C of the tile's tokens, read by every channel
+  float* ops = sm + TILE * 2 * NP;              // [4][TILE][SCAN_THREADS]: dt, dt * x, D * x, silu(z) of each thread's channel
   int b = blockIdx.x, ck = 0;
   if (MODE != 0 && !chunk_of(cu_q, n_seqs, cht, blockIdx.x, &b, &ck)) return;
   const int slot = seq_slot[b];
@@ -60,12 +79,14 @@ __global__ void __launch_bounds__(SCAN_THREADS) selscan_kernel(
   const int c = blockIdx.y * cpb + threadIdx.x / lpc;
   const bool live = c < inner;
   const int cc = live ? c : inner - 1;       // lanes beyond the last channel follow it (they take part in the shuffles) and store nothing
+  const int n0 = sub * NR;
 
-  float A[NR], S[NR];
+  // A2 = A log2(e): the decay exp(dt A) is one exp2 of a product
+  float A2[NR], S[NR];
 #pragma unroll
   for (int j = 0; j < NR; ++j) {
-    const int n = sub + j * lpc;
-    A[j] = n < N ? -expf(a_log[(size_t)cc * N + n]) : 0.f;
+    const int n = n0 + j;
+    A2[j] = n < N ? -expf(a_log[(size_t)cc * N + n]) * 1.4426950408889634f : 0.f;
     S[j] = 0.f;
     if (n < N) {
       if (MODE == 0) S[j] = state[((size_t)slot * inner + cc) * N + n];
@@ -74,66 +95,82 @@ __global__ void __launch_bounds__(SCAN_THREADS) selscan_kernel(
   }
   const float bias = dt_bias[cc], dsk = Dp[cc];
   float sum_dt = 0.f;
+  float* my = ops + threadIdx.x;
 
-  // the first token's operands
-  float n_dt = dtp[(size_t)t0 * inner + cc], n_x = xc[(size_t)t0 * inner + cc], n_z = 0.f;
-  float n_B[NR], n_C[NR];
+  for (int tb = t0; tb < t1; tb += TILE) {
+    const int cnt = min(TILE, t1 - tb);
+    __syncthreads();                           // the tile before is used up
+    for (int i = threadIdx.x; i < cnt * 2 * NP; i += SCAN_THREADS) {
+      const int tt = i / (2 * NP), e = i - tt * 2 * NP, n = e < NP ? e : e - NP;
+      bc[i] = n < N ? low[(size_t)(tb + tt) * low_ld + (e < NP ? b_off : c_off) + n] : 0.f;
+    }
+    // this channel's operands of the tile's tokens: every load is in flight before the first is used
+    float dtv[TILE], xv[TILE], zv[TILE];
 #pragma unroll
-  for (int j = 0; j < NR; ++j) {
-    const int n = sub + j * lpc;
-    n_B[j] = n < N ? low[(size_t)t0 * low_ld + b_off + n] : 0.f;
-    n_C[j] = (MODE != 1 && n < N) ? low[(size_t)t0 * low_ld + c_off + n] : 0.f;
-  }
-  if (MODE != 1) n_z = zrows[(size_t)t0 * z_ld + z_off + cc];
-
-  for (int t = t0; t < t1; ++t) {
-    const float dt_raw = n_dt, xv = n_x, zv = n_z;
-    float Bv[NR], Cv[NR];
+    for (int tt = 0; tt < TILE; ++tt) {
+      const size_t t = (size_t)tb + (tt < cnt ? tt : 0);
+      dtv[tt] = dtp[t * inner + cc];
+      xv[tt] = xc[t * inner + cc];
+      zv[tt] = MODE != 1 ? zrows[t * z_ld + z_off + cc] : 0.f;
+    }
 #pragma unroll
-    for (int j = 0; j < NR; ++j) { Bv[j] = n_B[j]; Cv[j] = n_C[j]; }
-    if (t + 1 < t1) {
-      const size_t tn = (size_t)t + 1;
-      n_dt = dtp[tn * inner + cc];
-      n_x = xc[tn * inner + cc];
-      if (MODE != 1) n_z = zrows[tn * z_ld + z_off + cc];
-#pragma unroll
-      for (int j = 0; j < NR; ++j) {
-        const int n = sub + j * lpc;
-        n_B[j] = n < N ? low[tn * low_ld + b_off + n] : 0.f;
-        if (MODE != 1) n_C[j] = n < N ? low[tn * low_ld + c_off + n] : 0.f;
+    for (int tt = 0; tt < TILE; ++tt) {
+      const float dt = softplus_(dtv[tt] + bias);
+      my[(0 * TILE + tt) * SCAN_THREADS] = dt;
+      my[(1 * TILE + tt) * SCAN_THREADS] = dt * xv[tt];
+      if (MODE != 1) {
+        my[(2 * TILE + tt) * SCAN_THREADS] = dsk * xv[tt];
+        my[(3 * TILE + tt) * SCAN_THREADS] = zv[tt] / (1.f + expf(-zv[tt]));
       }
     }
-    const float dt = softplus_(dt_raw + bias);
-    const float dtx = dt * xv;
-    sum_dt += dt;
-    float acc = 0.f;
+    __syncthreads();
+#pragma unroll 2
+    for (int tt = 0; tt < cnt; ++tt) {
+      const float dt = my[(0 * TILE + tt) * SCAN_THREADS], dtx = my[(1 * TILE + tt) * SCAN_THREADS];
+      sum_dt += dt;
+      const float* Bv = bc + tt * 2 * NP + n0;
+      const float* Cv = Bv + NP;
+      float acc = 0.f;
+      if (NR % 4 == 0) {
 #pragma unroll
-    for (int j = 0; j < NR; ++j) {
-      S[j] = fmaf(expf(dt * A[j]), S[j], dtx * Bv[j]);
-      acc = fmaf(S[j], Cv[j], acc);
-    }
-    if (MODE != 1) {
-      for (int o = lpc >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (sub == 0 && live) {
-        const float y = fmaf(dsk, xv, acc);
-        out[(size_t)t * inner + c] = from_f32<T>(y * (zv / (1.f + expf(-zv))));
+        for (int j = 0; j < NR; j += 4) {
+          const float4 b4 = *reinterpret_cast<const float4*>(Bv + j);
+          const float bb[4] = {b4.x, b4.y, b4.z, b4.w};
+          float cv[4] = {0.f, 0.f, 0.f, 0.f};
+          if (MODE != 1) {
+            const float4 c4 = *reinterpret_cast<const float4*>(Cv + j);
+            cv[0] = c4.x; cv[1] = c4.y; cv[2] = c4.z; cv[3] = c4.w;
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            S[j + u] = fmaf(exp2_neg(dt * A2[j + u]), S[j + u], dtx * bb[u]);
+            if (MODE != 1) acc = fmaf(S[j + u], cv[u], acc);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < NR; ++j) {
+          S[j] = fmaf(exp2_neg(dt * A2[j]), S[j], dtx * Bv[j]);
+          if (MODE != 1) acc = fmaf(S[j], Cv[j], acc);
+        }
+      }
+      if (MODE != 1) {
+        for (int o = lpc >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (sub == 0 && live)
+          out[(size_t)(tb + tt) * inner + c] = from_f32<T>((acc + my[(2 * TILE + tt) * SCAN_THREADS]) * my[(3 * TILE + tt) * SCAN_THREADS]);
       }
     }
   }
   if (!live) return;
   if (MODE == 0) {
 #pragma unroll
-    for (int j = 0; j < NR; ++j) {
-      const int n = sub + j * lpc;
-      if (n < N) state[((size_t)slot * inner + c) * N + n] = S[j];
-    }
+    for (int j = 0; j < NR; ++j)
+      if (n0 + j < N) state[((size_t)slot * inner + c) * N + n0 + j] = S[j];
   }
   if (MODE == 1) {
 #pragma unroll
-    for (int j = 0; j < NR; ++j) {
-      const int n = sub + j * lpc;
-      if (n < N) cstate[((size_t)blockIdx.x * inner + c) * N + n] = S[j];
-    }
+    for (int j = 0; j < NR; ++j)
+      if (n0 + j < N) cstate[((size_t)blockIdx.x * inner + c) * N + n0 + j] = S[j];
     if (sub == 0) cdt[(size_t)blockIdx.x * inner + c] = sum_dt;
   }
 }
@@ -151,13 +188,13 @@ __global__ void __launch_bounds__(256) selscan_prefix_kernel(
   int first = 0;
   for (int i = 0; i < b; ++i) first += (cu_q[i + 1] - cu_q[i] + cht - 1) / cht;
   const int nc = (cu_q[b + 1] - cu_q[b] + cht - 1) / cht;
-  const float A = -expf(a_log[e]);
+  const float A2 = -expf(a_log[e]) * 1.4426950408889634f;      // as in the scan: the decay is one exp2 of a product
   float S = state[(size_t)slot * inner * N + e];
   for (int k = 0; k < nc; ++k) {
     const size_t at = (size_t)(first + k) * inner * N + e;
     const float own = cstate[at];
     cstate[at] = S;
-    S = fmaf(expf(A * cdt[(size_t)(first + k) * inner + c]), S, own);
+    S = fmaf(exp2_neg(A2 * cdt[(size_t)(first + k) * inner + c]), S, own);
   }
   state[(size_t)slot * inner * N + e] = S;
 }
@@ -171,7 +208,8 @@ template <typename T, int MODE, int NR>
 int launch_mode(const Args& a, int blocks_x, cudaStream_t st) {
   const int cpb = SCAN_THREADS / a.lpc;
   dim3 grid(blocks_x, (a.inner + cpb - 1) / cpb);
-  selscan_kernel<T, MODE, NR><<<grid, SCAN_THREADS, 0, st>>>(a.xc, a.low, a.low_ld, a.b_off, a.c_off, a.dtp, a.dt_bias, a.a_log, a.Dp,
+  const size_t smem = sizeof(float) * ((size_t)TILE * 2 * NR * a.lpc + 4 * TILE * SCAN_THREADS);
+  selscan_kernel<T, MODE, NR><<<grid, SCAN_THREADS, smem, st>>>(a.xc, a.low, a.low_ld, a.b_off, a.c_off, a.dtp, a.dt_bias, a.a_log, a.Dp,
                                                             a.zrows, a.z_ld, a.z_off, a.cu_q, a.seq_slot, a.n_seqs, a.cht, a.inner, a.N,
                                                             a.lpc, a.state, a.cstate, a.cdt, (T*)a.out);
   return launch_status();
@@ -200,7 +238,7 @@ DRYFT_API int dryft_selscan(int out_bf16, const float* xc, const float* low, int
   if (n_seqs <= 0) return 0;
   if (inner <= 0 || N <= 0 || N > 512 || (n_chunks > 0 && (cht <= 0 || !cstate || !cdt))) return DRYFT_ERR_UNSUPPORTED;
   int lpc = 1;
-  while (lpc < 32 && (N + lpc - 1) / lpc > 4) lpc *= 2;     // four states a lane where the state allows it
+  while (lpc < 32 && (N + lpc - 1) / lpc > 16) lpc *= 2;    // a thread a channel while its states fit sixteen registers
   const int nr = (N + lpc - 1) / lpc;
   Args a{xc, low, low_ld, b_off, c_off, dtp, dt_bias, a_log, Dp, zrows, z_ld, z_off, cu_q, seq_slot, n_seqs, cht, inner, N, lpc,
          state, cstate, cdt, out};
@@ -209,7 +247,9 @@ DRYFT_API int dryft_selscan(int out_bf16, const float* xc, const float* low, int
   if (nr <= 1) { DRYFT_SELSCAN(1); }
   if (nr <= 2) { DRYFT_SELSCAN(2); }
   if (nr <= 4) { DRYFT_SELSCAN(4); }
+  if (nr <= 6) { DRYFT_SELSCAN(6); }
   if (nr <= 8) { DRYFT_SELSCAN(8); }
+  if (nr <= 12) { DRYFT_SELSCAN(12); }
   DRYFT_SELSCAN(16);
 #undef DRYFT_SELSCAN
 }

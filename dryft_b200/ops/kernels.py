@@ -2005,7 +2005,7 @@ def softcap(logits, cap: float) -> None:
 
 # ----------------------------------------------------------------------------- selective scan (a decay per channel and state)
 SELSCAN_MAX_STATE = 512
-SELSCAN_CHUNK_TOKENS = 128
+SELSCAN_CHUNK_TOKENS = 64
 
 
 def selscan_lib() -> ctypes.CDLL:
