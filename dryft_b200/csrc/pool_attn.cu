@@ -36,6 +36,7 @@ constexpr int DR = (D + 31) / 32, DVR = (DV + 31) / 32;
 constexpr int ROWS_WARPS = 4;
 constexpr int BLOCKS_THREADS = (D + DV + 31) / 32 * 32 < 1024 ? (D + DV + 31) / 32 * 32 : 1024;   // a thread a column of a key or a value
 constexpr int PREP_WARPS = 4;
+constexpr int PREP_TOK_WARPS = 8;    // pool_attn_prep_tok: a block a token, its vectors dealt to the warps
 
 // sin and cos of  pos * (f_hi + f_lo): the product is formed in 32-bit, and what its rounding drops (recovered exactly with
 // one fused multiply-add) plus the low half of the frequency are applied as a first-order turn.  f_lo = 0 gives the plain
@@ -121,12 +122,12 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) pool_attn_prep_kernel(
 
 // One block per token.  q_w [H * D] / k_w [G * D]: the weights of a norm over the whole projection (nullptr: no such norm).
 template <typename T>
-__global__ void __launch_bounds__(PREP_WARPS * 32) pool_attn_prep_tok_kernel(
+__global__ void __launch_bounds__(PREP_TOK_WARPS * 32) pool_attn_prep_tok_kernel(
     const T* __restrict__ proj, int ld, const float* __restrict__ q_w, const float* __restrict__ k_w, float norm_eps,
     const float* __restrict__ inv_freq, const float* __restrict__ inv_freq_lo, int rot, int interleaved, const int* __restrict__ tok_slot,
     const int* __restrict__ tok_pos, T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
     const int* __restrict__ page_table, int max_pages, int page_size, int H, int G, float eps, int write_kv) {
-  __shared__ float sm[PREP_WARPS][D];
+  __shared__ float sm[PREP_TOK_WARPS][D];
   __shared__ float scratch[33];
   const int t = blockIdx.x;
   const int slot = tok_slot[t];
@@ -137,12 +138,12 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) pool_attn_prep_tok_kernel(
   float rq = 1.f, rk = 1.f;
   if (q_w != nullptr) {
     float a = 0.f;
-    for (int c = threadIdx.x; c < H * D; c += PREP_WARPS * 32) { const float v = to_f32<T>(row[c]); a = fmaf(v, v, a); }
+    for (int c = threadIdx.x; c < H * D; c += PREP_TOK_WARPS * 32) { const float v = to_f32<T>(row[c]); a = fmaf(v, v, a); }
     rq = 1.f / sqrtf(block_sum(a, scratch) / (float)(H * D) + norm_eps);
   }
   if (k_w != nullptr && write_kv) {
     float a = 0.f;
-    for (int c = threadIdx.x; c < G * D; c += PREP_WARPS * 32) { const float v = to_f32<T>(row[(size_t)H * D + c]); a = fmaf(v, v, a); }
+    for (int c = threadIdx.x; c < G * D; c += PREP_TOK_WARPS * 32) { const float v = to_f32<T>(row[(size_t)H * D + c]); a = fmaf(v, v, a); }
     rk = 1.f / sqrtf(block_sum(a, scratch) / (float)(G * D) + norm_eps);
   }
   size_t cache_row0 = 0;
@@ -151,7 +152,7 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) pool_attn_prep_tok_kernel(
   const int half = rot / 2;
   const float fpos = (float)pos;
   float* s = sm[warp];
-  for (int vec = warp; vec < per_tok; vec += PREP_WARPS) {
+  for (int vec = warp; vec < per_tok; vec += PREP_TOK_WARPS) {
     if (vec >= H + G) {     // a value vector: into the cache as it is
       const int g = vec - H - G;
       const size_t cr = (cache_row0 * G + g) * page_size + pos % page_size;
@@ -457,11 +458,11 @@ DRYFT_API int dryft_pool_attn_prep_tok(int is_bf16, const void* proj, int ld, co
     return DRYFT_ERR_UNSUPPORTED;
   typedef __nv_bfloat16 bf;
   if (is_bf16)
-    pool_attn_prep_tok_kernel<bf><<<n, PREP_WARPS * 32, 0, st>>>((const bf*)proj, ld, q_w, k_w, norm_eps, inv_freq, inv_freq_lo, rot, interleaved,
+    pool_attn_prep_tok_kernel<bf><<<n, PREP_TOK_WARPS * 32, 0, st>>>((const bf*)proj, ld, q_w, k_w, norm_eps, inv_freq, inv_freq_lo, rot, interleaved,
                                                                  tok_slot, tok_pos, (bf*)q_out, (bf*)k_pages, (bf*)v_pages, page_table, max_pages,
                                                                  page_size, H, G, eps, write_kv);
   else
-    pool_attn_prep_tok_kernel<float><<<n, PREP_WARPS * 32, 0, st>>>((const float*)proj, ld, q_w, k_w, norm_eps, inv_freq, inv_freq_lo, rot,
+    pool_attn_prep_tok_kernel<float><<<n, PREP_TOK_WARPS * 32, 0, st>>>((const float*)proj, ld, q_w, k_w, norm_eps, inv_freq, inv_freq_lo, rot,
                                                                     interleaved, tok_slot, tok_pos, (float*)q_out, (float*)k_pages,
                                                                     (float*)v_pages, page_table, max_pages, page_size, H, G, eps, write_kv);
   return launch_status();

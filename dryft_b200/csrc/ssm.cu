@@ -10,7 +10,7 @@
 // [slots, heads, N, dv], and the convolution's last taps - 1 inputs `tail` [slots, taps - 1, CH].  A prompt, a piece of
 // one and a single token are the same operation.
 //
-//   ssm_conv    out[t, c] = silu(cb[c] + sum_j cw[c, j] * in[t - (taps - 1) + j, c]); inputs before the step's first
+//   ssm_conv    out[t, c] = silu(cb[c] + sum_j cw[c, j] * in[t - (taps - 1) + j, c]) (and, if asked, a bfloat16 copy); inputs before the step's first
 //               token come from the tail (zeros before the sequence's start).  A thread a (token, channel).
 //   ssm_tail    the tail after the step (run after ssm_conv, which reads the old one).  A thread a (sequence, channel).
 //   ssm_scan    one block per (sequence, head, slice of WARPS x COLS value columns); a warp owns COLS columns of S, a lane the
@@ -44,7 +44,7 @@ __device__ __forceinline__ int seq_of(const int* __restrict__ cu_q, int n_seqs, 
 __global__ void __launch_bounds__(CONV_THREADS) ssm_conv_kernel(
     const float* __restrict__ proj, int ld, int x_off, int CH, const int* __restrict__ cu_q, const int* __restrict__ seq_slot,
     int n_seqs, const float* __restrict__ cw, const float* __restrict__ cb, int taps, const float* __restrict__ tail,
-    float* __restrict__ out) {
+    float* __restrict__ out, __nv_bfloat16* __restrict__ out_bf16) {
   const int t = blockIdx.x;
   const int b = seq_of(cu_q, n_seqs, t);
   const int slot = seq_slot[b];
@@ -59,7 +59,9 @@ __global__ void __launch_bounds__(CONV_THREADS) ssm_conv_kernel(
                                : tail[((size_t)slot * (taps - 1) + (taps - 1 + src)) * CH + c];
       acc = fmaf(cw[(size_t)c * taps + j], v, acc);
     }
-    out[(size_t)t * CH + c] = acc / (1.f + expf(-acc));
+    const float v = acc / (1.f + expf(-acc));
+    out[(size_t)t * CH + c] = v;
+    if (out_bf16 != nullptr) out_bf16[(size_t)t * CH + c] = __float2bfloat16_rn(v);   // the operand of a bfloat16 product behind it
   }
 }
 
@@ -222,12 +224,14 @@ __global__ void __launch_bounds__(256) ssm_chunk_prefix_kernel(const int* __rest
 }  // namespace
 
 DRYFT_API int dryft_ssm_conv(const float* proj, int ld, int x_off, int CH, const int* cu_q, const int* seq_slot, int n_seqs,
-                             const float* cw, const float* cb, int taps, float* tail, float* out, int n_tokens, cudaStream_t st) {
+                             const float* cw, const float* cb, int taps, float* tail, float* out, void* out_bf16, int n_tokens,
+                             cudaStream_t st) {
   if (n_tokens <= 0 || n_seqs <= 0) return 0;
   if (taps < 1 || taps > MAX_TAPS || CH < 1 || (taps > 1 && tail == nullptr)) return DRYFT_ERR_UNSUPPORTED;
   const dim3 grid_c(n_tokens, (CH + CONV_THREADS - 1) / CONV_THREADS), grid_t(n_seqs, (CH + CONV_THREADS - 1) / CONV_THREADS);
   if (grid_c.y > 65535) return DRYFT_ERR_UNSUPPORTED;
-  ssm_conv_kernel<<<grid_c, CONV_THREADS, 0, st>>>(proj, ld, x_off, CH, cu_q, seq_slot, n_seqs, cw, cb, taps, tail, out);
+  ssm_conv_kernel<<<grid_c, CONV_THREADS, 0, st>>>(proj, ld, x_off, CH, cu_q, seq_slot, n_seqs, cw, cb, taps, tail, out,
+                                                   (__nv_bfloat16*)out_bf16);
   int rc = launch_status();
   if (rc || taps == 1) return rc;
   ssm_tail_kernel<<<grid_t, CONV_THREADS, 0, st>>>(proj, ld, x_off, CH, cu_q, seq_slot, taps, tail);

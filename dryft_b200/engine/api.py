@@ -56,6 +56,10 @@ class EngineOptions:
     # evaluation.  Off by default: the default path keeps the reference's rounding points.
     norm_ahead: bool = False
     tcgen05: bool = True                   # prefill attention on tcgen05 / TMEM / TMA where the head size allows
+    # steps of up to this many rows run sublayers that read the same input (a mixer beside a feed-forward, two mixers side
+    # by side) on streams of their own, joined before their results are summed: in a captured step they are parallel
+    # branches of the graph.  0: one after another.  The results are the same bits either way.
+    branch_rows: int = 16
     # Prompts longer than this go through the step function in chunks of this many tokens per sequence (the same
     # step again, from the cache the chunk before left): bounds the step's activations ([tokens, q + 2 kv], the
     # attention output) whatever the prompt length.  None: whole prompts in one step.
@@ -118,7 +122,8 @@ class Engine:
         self.dtype = dtype
         props = torch.cuda.get_device_properties(dev)
         self.rt = Runtime(dtype=dtype, device=dev, page_size=opts.page_size, sm_count=props.multi_processor_count,
-                          small_m_max=opts.small_m_max, stream_m_max=opts.stream_m_max, fuse_decode=opts.fuse_decode, pdl=opts.pdl, tcgen05=opts.tcgen05, norm_ahead=opts.norm_ahead)
+                          small_m_max=opts.small_m_max, stream_m_max=opts.stream_m_max, fuse_decode=opts.fuse_decode, pdl=opts.pdl, tcgen05=opts.tcgen05, norm_ahead=opts.norm_ahead,
+                          branch_rows=opts.branch_rows)
         with torch.cuda.device(dev), torch.no_grad():
             self.model = DecoderModel(spec, source, self.rt)
             self.max_seq_len = opts.max_seq_len or min(spec.max_positions, 8192)

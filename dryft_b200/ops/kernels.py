@@ -1684,7 +1684,7 @@ SSM_MAX_TAPS = 16
 
 def ssm_lib() -> ctypes.CDLL:
     return _single_lib("ssm", {
-        "dryft_ssm_conv": [_p, _i, _i, _i, _p, _p, _i, _p, _p, _i, _p, _p, _i, _p],
+        "dryft_ssm_conv": [_p, _i, _i, _i, _p, _p, _i, _p, _p, _i, _p, _p, _p, _i, _p],
         "dryft_ssm_scan": [_p, _i, _p, _i, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p, _p],
         "dryft_ssm_scan_chunked": [_p, _i, _p, _i, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p],
     })
@@ -1693,16 +1693,19 @@ def ssm_lib() -> ctypes.CDLL:
 SSM_CHUNK_TOKENS = 128    # tokens a chunk of a many-token step walks in order (more for steps of more than 8,192 tokens)
 
 
-def ssm_conv(proj, x_off: int, conv_w, conv_b, cu_q, seq_slot, n_seqs: int, tail, out) -> None:
+def ssm_conv(proj, x_off: int, conv_w, conv_b, cu_q, seq_slot, n_seqs: int, tail, out, out_bf16=None) -> None:
     """``out[t, c] = silu(conv_b[c] + sum_j conv_w[c, j] * in[t - (taps-1) + j, c])`` over the ``C`` channels of ``proj [n, ld]``
     (float32) from column ``x_off``; inputs from before the step come from ``tail [slots, taps-1, C]``, which is then
-    advanced.  Two launches (one when there is a single tap)."""
+    advanced.  Two launches (one when there is a single tap).  ``out_bf16``: the same values once more, rounded (the operand of
+    a bfloat16 product that follows)."""
     n, ld = proj.shape
     c, taps = conv_w.shape
     _need(proj, "proj", torch.float32)
     _need(conv_w, "conv_w", torch.float32)
     _need(conv_b, "conv_b", torch.float32, (c,))
     _need(out, "out", torch.float32, (n, c))
+    if out_bf16 is not None:
+        _need(out_bf16, "out_bf16", torch.bfloat16, (n, c))
     if x_off < 0 or x_off + c > ld:
         raise KernelError(f"ssm_conv: {c} channels from column {x_off} of a row of {ld}")
     if taps > 1:
@@ -1710,7 +1713,7 @@ def ssm_conv(proj, x_off: int, conv_w, conv_b, cu_q, seq_slot, n_seqs: int, tail
     for t, nm in ((cu_q, "cu_q"), (seq_slot, "seq_slot")):
         _need(t, nm, torch.int32)
     _ok(ssm_lib().dryft_ssm_conv(_ptr(proj), ld, int(x_off), c, _ptr(cu_q), _ptr(seq_slot), int(n_seqs), _ptr(conv_w), _ptr(conv_b),
-                                 taps, _ptr(tail if taps > 1 else None), _ptr(out), n, _stream()),
+                                 taps, _ptr(tail if taps > 1 else None), _ptr(out), _ptr(out_bf16), n, _stream()),
         f"ssm_conv ({c} channels, {taps} taps)", n_kernels=2 if taps > 1 else 1)
 
 

@@ -63,6 +63,37 @@ class Runtime:
     pdl: bool = True             # launch the fused decode products as programmatic dependents
     norm_ahead: bool = False     # fused decode: a residual product leaves the stream weighted for the next norm (one rounding fewer than the reference)
     tcgen05: bool = True         # prompts: attention on tcgen05.mma / tensor memory / TMA where sizes allow
+    branch_rows: int = 0         # steps of up to this many rows run independent sublayers on streams of their own (0: in turn)
+    side_streams: list = field(default_factory=list, repr=False, compare=False)
+
+    def branches(self, n_rows: int) -> bool:
+        return bool(self.branch_rows) and n_rows <= self.branch_rows and self.device.type == "cuda"
+
+    def run_branches(self, jobs, first_stream: int = 0) -> list:
+        """Run ``jobs`` (callables without arguments that read the same inputs): the first on the current stream, each
+        other on a side stream that starts where the current stream stands and is joined before this returns.  In a captured
+        step these are parallel branches of the graph; eagerly they overlap as far as the device allows.  Tensors made on
+        a side stream are safe to use and drop on the current one afterwards: the next fork is recorded behind their use."""
+        if len(jobs) == 1:
+            return [jobs[0]()]
+        main = torch.cuda.current_stream(self.device)
+        while len(self.side_streams) < first_stream + len(jobs) - 1:
+            self.side_streams.append(torch.cuda.Stream(self.device))
+        fork = torch.cuda.Event()
+        fork.record(main)
+        out, joins = [None] * len(jobs), []
+        for i, job in enumerate(jobs[1:], 1):
+            side = self.side_streams[first_stream + i - 1]
+            with torch.cuda.stream(side):
+                side.wait_event(fork)
+                out[i] = job()
+                done = torch.cuda.Event()
+                done.record(side)
+            joins.append(done)
+        out[0] = jobs[0]()
+        for done in joins:
+            main.wait_event(done)
+        return out
 
     @property
     def is_bf16(self) -> bool:

@@ -225,7 +225,8 @@ class ParallelBlock:
     ``forward_terms`` (two mixers side by side) hands over its results unsummed with their factors, a routed feed-forward
     whose weights are already inside its experts (``sums_plainly``) its ``top`` rows per token; the same kernel leaves the
     stream normed for the layer that runs next when that layer's norm is known (``next_norm``), so a layer is one norm-less
-    chain of products and one sum.  There is no second norm (``norm_ffn`` must be None); a layer without a feed-forward
+    chain of products and one sum; in a step of few rows the feed-forward runs beside the mixer on a stream of its own
+    (``Runtime.run_branches``).  There is no second norm (``norm_ffn`` must be None); a layer without a feed-forward
     adds the mixer's result alone."""
 
     takes_next_norm = True
@@ -249,14 +250,26 @@ class ParallelBlock:
         if res.delta is not None:
             x.add_(res.delta)
         n = res.hn if (res.hn is not None and res.hn_norm is self.norm_mixer) else self.norm_mixer.forward(x)
-        terms = getattr(self.mixer, "forward_terms", None)
-        terms = terms(n, ctx, cache, state, owns_cache) if terms is not None else [(self.mixer.forward(n, ctx, cache, state, owns_cache), 1.0)]
-        rows, top = None, 0
-        if self.ffn is not None:
+        def mix():
+            terms = getattr(self.mixer, "forward_terms", None)
+            return list(terms(n, ctx, cache, state, owns_cache)) if terms is not None else [(self.mixer.forward(n, ctx, cache, state, owns_cache), 1.0)]
+
+        def feed():
             if getattr(self.ffn, "sums_plainly", False):
-                rows, top = self.ffn.forward_rows(n, ctx)
+                return self.ffn.forward_rows(n, ctx)
+            return self.ffn.forward(n, ctx)
+
+        rt = self.mixer.rt
+        rows, top = None, 0
+        if self.ffn is None:
+            terms = mix()
+        else:
+            # few rows: the feed-forward runs beside the mixer on a stream of its own (both read the same normed rows)
+            terms, f = rt.run_branches([mix, feed], first_stream=0) if rt.branches(x.shape[0]) else (mix(), feed())
+            if isinstance(f, tuple):
+                rows, top = f
             else:
-                terms = list(terms) + [(self.ffn.forward(n, ctx), 1.0)]
+                terms = terms + [(f, 1.0)]
         plain = self._plain(next_norm) if next_norm is not None else None
         hn = None
         if plain is not None:

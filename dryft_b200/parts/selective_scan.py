@@ -84,8 +84,10 @@ class SelectiveScan:
         R, N = self.dt_rank, self.n_state
         proj = linear(h, self.w_in, self.rt, out_dtype=torch.float32)            # [n, x | z], 32-bit sums kept
         xc = torch.empty((n, self.inner), dtype=torch.float32, device=dev)
-        K.ssm_conv(proj, 0, self.conv_w, self.conv_b, ctx.cu_q, ctx.seq_slot, ctx.n_seqs, state.get("tail"), xc)
-        low = linear(xc if h.dtype == torch.float32 else xc.to(h.dtype), self.w_x, self.rt, out_dtype=torch.float32)   # [n, d | B | C]
+        xc_act = xc if h.dtype == torch.float32 else torch.empty((n, self.inner), dtype=h.dtype, device=dev)
+        K.ssm_conv(proj, 0, self.conv_w, self.conv_b, ctx.cu_q, ctx.seq_slot, ctx.n_seqs, state.get("tail"), xc,
+                   out_bf16=None if xc_act is xc else xc_act)
+        low = linear(xc_act, self.w_x, self.rt, out_dtype=torch.float32)         # [n, d | B | C]
         d = low[:, :R].contiguous() if h.dtype == torch.float32 else low[:, :R].to(h.dtype)
         dtp = linear(d, self.w_dt, self.rt, out_dtype=torch.float32)             # step sizes before bias and softplus
         out = torch.empty((n, self.inner), dtype=h.dtype, device=dev)

@@ -76,11 +76,14 @@ class SideBySide:
 
     def forward_terms(self, h: torch.Tensor, ctx: StepContext, cache, state, owns_cache: bool = True) -> List[Tuple[torch.Tensor, float]]:
         """``[(left(h), left_scale), (right(h), right_scale)]``: the caller forms the sum."""
-        terms = []
-        for side, part in self.parts.items():
-            y = part.forward(h, ctx, cache if side == self.kv_side else None, self._state_of(side, state), owns_cache)
-            terms.append((y, self.scales[side]))
-        return terms
+        def job(side):
+            part = self.parts[side]
+            return lambda: part.forward(h, ctx, cache if side == self.kv_side else None, self._state_of(side, state), owns_cache)
+
+        jobs = [job(side) for side in _SIDES]
+        # few rows: the two mixers run on streams of their own (the first side stream is the enclosing arrangement's)
+        ys = self.rt.run_branches(jobs, first_stream=1) if self.rt.branches(h.shape[0]) else [j() for j in jobs]
+        return [(y, self.scales[side]) for y, side in zip(ys, _SIDES)]
 
     def forward(self, h: torch.Tensor, ctx: StepContext, cache, state, owns_cache: bool = True) -> torch.Tensor:
         terms = self.forward_terms(h, ctx, cache, state, owns_cache)

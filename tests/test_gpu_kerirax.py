@@ -287,6 +287,32 @@ def test_forty_unequal_requests_at_once(tmp_path_factory, dtype):
     eng.cache.check()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_sublayers_on_streams_of_their_own_give_the_same_bits(tmp_path_factory, dtype):
+    """Few-row steps run the feed-forward beside the mixer, and the two mixers of a pair beside each other, on side streams
+    (parallel branches of a captured step): the logits are the same bits as with everything in turn, eagerly and replayed."""
+    entry = model("looped", tmp_path_factory)
+    cfg = entry[0]
+    reqs = M.prompts(cfg, [70, 31, 2, 9], seed=14)
+    rows = {}
+    for branch in (16, 0):
+        eng = engine(entry, dtype, branch_rows=branch)
+        with torch.inference_mode():
+            slots = eng.cache.open_sequences(len(reqs))
+            got = [eng.stepper.step(slots, reqs, [[len(t) - 1] for t in reqs])]     # four rows wanted of a step of many
+            for t in range(20):
+                got.append(eng.stepper.step(slots, [[(7 * t + b) % cfg["vocab"]] for b in range(len(reqs))], [[0]] * len(reqs)))
+            eng.cache.close_sequences(slots)
+            torch.cuda.synchronize()
+        rows[branch] = torch.cat(got).cpu()
+        toks = engine(entry, dtype, branch_rows=branch, cuda_graphs=True, max_batch=4).generate_many(reqs, 10)
+        rows[("tokens", branch)] = toks
+    assert torch.equal(rows[16], rows[0])
+    assert rows[("tokens", 16)] == rows[("tokens", 0)]
+    want = torch.cat([plain_logits(entry, t)[-1:] for t in reqs])
+    check(entry, rows[16][:len(reqs)], want, dtype, "prompts before the branched steps")
+
+
 def _random_config(seed):
     """A configuration drawn at random: layer kinds and order, every size, every constant, where the repeated stretch lies."""
     import random
