@@ -59,7 +59,7 @@ class EngineOptions:
     # steps of up to this many rows run sublayers that read the same input (a mixer beside a feed-forward, two mixers side
     # by side) on streams of their own, joined before their results are summed: in a captured step they are parallel
     # branches of the graph.  0: one after another.  The results are the same bits either way.
-    branch_rows: int = 16
+    branch_rows: int = 64
     # Prompts longer than this go through the step function in chunks of this many tokens per sequence (the same
     # step again, from the cache the chunk before left): bounds the step's activations ([tokens, q + 2 kv], the
     # attention output) whatever the prompt length.  None: whole prompts in one step.
