@@ -176,14 +176,14 @@ def _kerirax(width: int, heads: int, kv_heads: int, dim: int, inner: int, state:
     pair = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "rot": rot}, "left_scale": 1.0,
             "right": {"inner": inner, "state": state, "dt_rank": dt_rank, "conv": 4}, "right_scale": 1.0}
     lat = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": dim, "q_rank": q_rank, "kv_rank": kv_rank,
-           "scale": (dim + rot_dim) ** -0.5, "rot": {"dims": rot_dim, "base": 20000.0}}
+           "scale": (dim + rot_dim) ** -0.5, "rot": {"dims": rot_dim, "base": 10000.0}}
     out = []
     for i in range(stretch + tail):
         mlp = {"kind": "dense", "ff": ff * (top + 1)} if i == 0 else \
             {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": experts, "top": top}}
         out.append({"type": "latent_attention", "mixer": lat, "mlp": mlp} if i % 3 == 1 else {"type": "parallel", "mixer": pair, "mlp": mlp})
     return {"architecture": "Kerirax", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
-            "logit_softcap": 30.0, "loop": {"start": 0, "stop": stretch, "times": times}, "layers": out}
+            "logit_softcap": 50.0, "loop": {"start": 0, "stop": stretch, "times": times}, "layers": out}
 
 
 # Kerirax shapes with layers the size of a real model's, and beside each the closest design at equal size: the Mogelix shape

@@ -3,7 +3,8 @@ every mixer alone and mixed, stretches of layers run several times, whole prompt
 prompts in portions down to two tokens, unequal batches against each request alone, slots, states and pages used again
 (poisoned), long decoding across page edges, the first tokens, the stream after every layer run, greedy generation through
 ``Engine.generate`` / ``generate_many`` (captured graphs and eager), the replay program and the command line as child
-processes, configurations drawn at random; and the new kernels alone against the plain functions: the selective scan with a
+processes, configurations drawn at random, sublayers on streams of their own against everything in turn (the same
+bits); and the new kernels alone against the plain functions: the selective scan with a
 memory of hundreds of tokens (in order and in chunks), the latent attention's sink with one key that outweighs all others,
 the norm over whole projections with both rotation layouts, the router's sigmoid scores, the clamp's edges."""
 
@@ -571,6 +572,6 @@ def test_stream_sum_and_softcap():
     normed = P.rms_norm(want.cpu(), nw.double().cpu(), 1e-5)
     assert float((h.double().cpu() - normed).abs().max()) <= 0.02
     z = torch.randn(4, 33, device=dev) * 40.0
-    want = 30.0 * torch.tanh(z.double() / 30.0)
-    K.softcap(z, 30.0)
+    want = 25.0 * torch.tanh(z.double() / 25.0)
+    K.softcap(z, 25.0)
     assert float((z.double() - want).abs().max()) <= 1e-4
